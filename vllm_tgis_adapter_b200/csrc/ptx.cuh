@@ -74,7 +74,7 @@ __device__ __forceinline__ void mbar_wait(uint64_t* bar, uint32_t parity) {
 __device__ __forceinline__ void tma_prefetch_desc(const CUtensorMap* m) {
   asm volatile("prefetch.tensormap [%0];\n" ::"l"(reinterpret_cast<uint64_t>(m)) : "memory");
 }
-// 2D tiled load global->smem, completes on mbarrier (SASS: UTMALDG)
+// 2D tiled load global->smem, completes on mbarrier
 __device__ __forceinline__ void tma_load_2d(const CUtensorMap* m, uint64_t* bar, void* dst, int c0, int c1) {
   asm volatile(
       "cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes"
@@ -90,14 +90,14 @@ __device__ __forceinline__ void tma_load_2d_hint(const CUtensorMap* m, uint64_t*
       "l"(reinterpret_cast<uint64_t>(m)), "r"(smem_u32(bar)), "r"(c0), "r"(c1), "l"(policy)
       : "memory");
 }
-// 2D tile prefetch into L2 only (SASS: UTMAPF.L2): no smem destination, no completion tracking
+// 2D tile prefetch into L2 only: no smem destination, no completion tracking
 __device__ __forceinline__ void tma_prefetch_2d(const CUtensorMap* m, int c0, int c1) {
   asm volatile("cp.async.bulk.prefetch.tensor.2d.L2.global.tile [%0, {%1, %2}];\n" ::"l"(
                    reinterpret_cast<uint64_t>(m)),
                "r"(c0), "r"(c1)
                : "memory");
 }
-// 1D bulk copy global->smem (SASS: UBLKCP); size multiple of 16, both addresses 16B aligned
+// 1D bulk copy global->smem; size multiple of 16, both addresses 16B aligned
 __device__ __forceinline__ void bulk_load_1d(void* dst, const void* src, uint32_t bytes, uint64_t* bar) {
   asm volatile(
       "cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];\n" ::"r"(
@@ -140,14 +140,14 @@ __device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence:
 __device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory"); }
 
 // tcgen05.commit: arrive on an mbarrier once all previously issued MMAs of this thread retire
-// (implies tcgen05.fence::before_thread_sync). SASS: UTCBAR
+// (implies tcgen05.fence::before_thread_sync)
 __device__ __forceinline__ void tc_commit(uint64_t* bar) {
   asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];\n" ::"r"(
                    smem_u32(bar))
                : "memory");
 }
 
-// D[tmem] (+)= A[smem] * B[smem], kind::f16 (bf16/fp16 in, fp32 accumulate). SASS: UTCHMMA
+// D[tmem] (+)= A[smem] * B[smem], kind::f16 (bf16/fp16 in, fp32 accumulate)
 __device__ __forceinline__ void tc_mma_f16(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc,
                                            uint32_t accumulate) {
   asm volatile(
@@ -179,7 +179,7 @@ __host__ __device__ constexpr uint32_t make_idesc_bf16(uint32_t umma_m, uint32_t
          | ((umma_m >> 4) << 24); // m_dim
 }
 
-// TMEM -> registers: 32 lanes (this warp's sub-partition) x N consecutive 32-bit columns. SASS: LDTM
+// TMEM -> registers: 32 lanes (this warp's sub-partition) x N consecutive 32-bit columns
 __device__ __forceinline__ void tmem_ld_32x32b_x16(uint32_t taddr, uint32_t* r) {
   asm volatile(
       "tcgen05.ld.sync.aligned.32x32b.x16.b32 "
