@@ -39,7 +39,7 @@
 extern "C" {
 #endif
 
-#define TGIS_ABI_VERSION 7
+#define TGIS_ABI_VERSION 8
 #define TGIS_MAX_REQUEST_ID 96
 #define TGIS_MAX_TOPN 12 /* reference forces max_logprobs >= 11: tgis_utils/args.py:214-216 */
 #define TGIS_MAX_STOP_TOKEN_IDS 8
@@ -56,6 +56,12 @@ typedef struct tgis_engine tgis_engine;
  *          leaves every dot product unchanged.  Single GPU, no LoRA slots. */
 #define TGIS_ARCH_LLAMA 0
 #define TGIS_ARCH_OPT 1
+/*   PONENEX: a stack of per-layer described blocks (tgis_model_spec / tgis_layer_spec below) on an fp32 residual stream:
+ *          pre- and post-normed sublayers scaled by a residual multiplier, a latent-attention mixer (low-rank query and
+ *          key/value latents, one shared rotary key part, sliding window, sigmoid output gate per head) and an optional
+ *          mixture-of-experts feed-forward (biased top-k router, softmax over the chosen logits, gated shared expert).
+ *          Created with tgis_engine_create_spec; bf16 or fp32 operands.  Single GPU, no LoRA slots. */
+#define TGIS_ARCH_PONENEX 2
 
 /* Model + runtime configuration (bf16 decoder-only transformer; see TGIS_ARCH_*). */
 typedef struct tgis_config {
@@ -94,6 +100,35 @@ typedef struct tgis_config {
   int32_t arch;               /* TGIS_ARCH_LLAMA / TGIS_ARCH_OPT */
   int32_t reserved0;
 } tgis_config;
+
+/* Per-layer geometry for architectures whose layers are listed one by one (TGIS_ARCH_PONENEX); tgis_config carries hidden,
+ * vocab, max_model_len and the runtime limits, its head / ffn / rope fields are unused. */
+#define TGIS_MIXER_LATENT_ATTENTION 1
+#define TGIS_MLP_NONE 0
+#define TGIS_MLP_MOE 1
+typedef struct tgis_layer_spec {
+  int32_t mixer;        /* TGIS_MIXER_* */
+  int32_t heads, dim, rot_dim, vdim, kv_rank, q_rank; /* per head: dim unrotated + rot_dim rotated query/key dims, vdim values */
+  int32_t window;       /* position i sees j with 0 <= i - j < window; <= 0: all earlier positions */
+  int32_t rot_dims;     /* the first rot_dims of the rot_dim dims are rotated (pairs i, i + rot_dims / 2) */
+  float rot_base;
+  float scale;          /* softmax scale */
+  int32_t mlp;          /* TGIS_MLP_* */
+  int32_t experts, top, expert_ff;
+  int32_t shared_ff;    /* 0: no shared expert */
+  int32_t reserved;
+} tgis_layer_spec;
+#define TGIS_DTYPE_BF16 0 /* bf16 operands, fp32 accumulation; norms, softmax, routers and the residual sum in fp32 */
+#define TGIS_DTYPE_F32 1  /* everything in true fp32 (no TF32) */
+typedef struct tgis_model_spec {
+  int32_t n_layers;
+  int32_t dtype;        /* TGIS_DTYPE_* */
+  float embed_scale;    /* x = embed[token] * embed_scale */
+  float residual_mult;  /* x += residual_mult * post_norm(sublayer(pre_norm(x))) */
+  float norm_eps;
+  int32_t reserved;
+  const tgis_layer_spec* layers; /* [n_layers] */
+} tgis_model_spec;
 
 /* What the adapter's proto->SamplingParams mapping (grpc_server.py:508-628) hands to the engine. */
 typedef struct tgis_sampling_params {
@@ -194,6 +229,10 @@ const char* tgis_last_error(void);
 int tgis_abi_version(void);
 
 int tgis_engine_create(const tgis_config* cfg, tgis_engine** out);
+/* cfg->arch == TGIS_ARCH_PONENEX; parameter names: "embed", "head", "final.norm", "l<i>.norm1|norm1b|norm2|norm2b",
+ * "l<i>.mix.dq|dq.norm|uq|dkv|dkv.norm|uk|uv|g|o", "l<i>.mlp.router|router.b|e<j>.gate|e<j>.up|e<j>.down|shared.gate|
+ * shared.up|shared.down|shared.sg" (bf16 [out, in]; the engine widens them for TGIS_DTYPE_F32). */
+int tgis_engine_create_spec(const tgis_config* cfg, const tgis_model_spec* spec, tgis_engine** out);
 /* name: HF Llama parameter name ("model.layers.3.self_attn.q_proj.weight", "lm_head.weight", ...) or
  * "tgis.rope_cos_sin" ([max_model_len,128] bf16 = cos|sin); arch OPT: HF OPT parameter names
  * ("model.decoder.layers.3.self_attn.q_proj.bias", "model.decoder.embed_positions.weight" with >= max_model_len + 2 rows,
@@ -226,6 +265,22 @@ int tgis_engine_set_profiling(tgis_engine* e, int32_t on);
 int tgis_engine_max_model_len(tgis_engine* e);
 int tgis_engine_shutdown(tgis_engine* e);
 void tgis_engine_destroy(tgis_engine* e);
+
+/* Trace replay: feed GIVEN tokens through the engine's own step function (scheduler slots, block manager, the same kernels
+ * and batch layout as generation), sampling nothing.  One call = one step = one batch: entry i brings the next n_tokens of
+ * request request_id (admitted at its first entry: a sequence slot and cache blocks are taken from the engine's pools;
+ * a request may be left out of a step and go on later) and asks for the logits after its tokens want[0..n_want) (indices
+ * into this entry's tokens).  logits_out: fp32 [sum n_want, vocab] in entry / want order.  end_ids: requests that are
+ * finished after this step; their slot and blocks go back to the pools.  Not to be mixed with add_request traffic. */
+typedef struct tgis_trace_entry {
+  const char* request_id;
+  const int32_t* tokens;
+  int32_t n_tokens;
+  int32_t n_want;
+  const int32_t* want;
+} tgis_trace_entry;
+int tgis_engine_trace_step(tgis_engine* e, const tgis_trace_entry* entries, int32_t n_entries, const char* const* end_ids,
+                           int32_t n_end, float* logits_out);
 
 /* Synchronous driver used by bench.py / tests: run the step loop on the calling thread until every queued request has
  * finished (no engine thread needed).  Returns the number of steps, <0 on error.  Step wall/GPU times accumulate in

@@ -1,0 +1,270 @@
+// Attention over a cached low-rank latent (kernels.h, LatentGeom): every token leaves ONE cache row
+// [c (kv_rank) | k_rot (rot_dim)]; the per-head key and value up-projections are folded into the query and the output,
+// so all heads of a token score against -- and sum over -- the same rows of the paged cache:
+//   s_h(i, j) = scale * q_abs_h(i) . row(j),        o_lat_h(i) = sum_j softmax_j(s_h(i, .)) c(j)
+// with j causal and, for window > 0, inside the last `window` positions.  Softmax, its running maximum / sum and the
+// output accumulators are fp32; cache rows are read in their storage type and widened.
+//
+// latent_attn_kernel serves prompts, prompt portions and single decoded tokens alike: a CTA owns up to LATENT_PAIRS
+// (token, head) pairs of one sequence, walks the cache blocks its queries can see (block table; blocks wholly outside
+// the window are never touched), stages each 32-row block in shared memory once and lets every warp run two pairs
+// against it: lane = key for the scores, lane = latent dimension (strided by 32) for the weighted sum.  A query's
+// arithmetic depends only on its own position and on the block grid of its sequence, not on the tile or step it came in.
+#include <cfloat>
+
+#include "kernels.h"
+#include "launch.cuh"
+#include "ptx.cuh"
+
+namespace tgis {
+namespace {
+
+constexpr int LAT_THREADS = 256;
+constexpr int LAT_WARPS = LAT_THREADS / 32;
+static_assert(LATENT_PAIRS == 2 * LAT_WARPS, "two pairs per warp");
+
+__device__ __forceinline__ float warp_sum_f(float v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+  return v;
+}
+__device__ __forceinline__ float warp_max_f(float v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
+  return v;
+}
+template <int THREADS>
+__device__ __forceinline__ float block_sum_f(float v, float* red) {
+  v = warp_sum_f(v);
+  const int w = threadIdx.x >> 5, l = threadIdx.x & 31;
+  if (l == 0) red[w] = v;
+  __syncthreads();
+  float t = (l < THREADS / 32) ? red[l] : 0.f;
+  t = warp_sum_f(t);
+  __syncthreads();
+  return t;
+}
+__device__ __forceinline__ void st_any(void* out, int dt, size_t i, float v) {
+  if (dt == DT_BF16) reinterpret_cast<__nv_bfloat16*>(out)[i] = __float2bfloat16_rn(v);
+  else reinterpret_cast<float*>(out)[i] = v;
+}
+template <class T>
+__device__ __forceinline__ float widen(T v);
+template <>
+__device__ __forceinline__ float widen<float>(float v) { return v; }
+template <>
+__device__ __forceinline__ float widen<__nv_bfloat16>(__nv_bfloat16 v) { return __bfloat162float(v); }
+
+// "rotate half" over the first rot_dims entries of a rot_dim-long vector: entry i pairs with i + rot_dims / 2
+__device__ __forceinline__ float rotary_entry(const float* v, int j, int rot_dims, const float* cs) {
+  const int half = rot_dims / 2;
+  if (j >= rot_dims) return v[j];
+  if (j < half) return v[j] * cs[j] - v[j + half] * cs[half + j];
+  return v[j] * cs[j - half] + v[j - half] * cs[j];  // cs[j] with j >= half is sin(j - half)
+}
+
+constexpr int PREP_THREADS = 256;
+__global__ void __launch_bounds__(PREP_THREADS)
+latent_prep_kernel(const float* __restrict__ y, int ldy, LatentGeom g, const float* __restrict__ w_q,
+                   const float* __restrict__ w_kv, float eps, const int32_t* __restrict__ positions,
+                   const int32_t* __restrict__ slot_mapping, const float* __restrict__ cos_sin, void* __restrict__ cq,
+                   void* __restrict__ cache, int dtype, float* __restrict__ gate) {
+  __shared__ float red[PREP_THREADS / 32];
+  griddep_launch();
+  griddep_wait();
+  const int t = blockIdx.x;
+  const float* row = y + (size_t)t * ldy;
+  const float* yq = row;
+  const float* ykv = row + g.q_rank;
+  const float* ykr = ykv + g.kv_rank;
+  const float* yg = ykr + g.rot_dim;
+  float ss = 0.f;
+  for (int i = threadIdx.x; i < g.q_rank; i += PREP_THREADS) ss += yq[i] * yq[i];
+  const float rs_q = 1.f / sqrtf(block_sum_f<PREP_THREADS>(ss, red) / (float)g.q_rank + eps);
+  ss = 0.f;
+  for (int i = threadIdx.x; i < g.kv_rank; i += PREP_THREADS) ss += ykv[i] * ykv[i];
+  const float rs_kv = 1.f / sqrtf(block_sum_f<PREP_THREADS>(ss, red) / (float)g.kv_rank + eps);
+  for (int i = threadIdx.x; i < g.q_rank; i += PREP_THREADS) st_any(cq, dtype, (size_t)t * g.q_rank + i, yq[i] * rs_q * w_q[i]);
+  if (gate != nullptr)
+    for (int h = threadIdx.x; h < g.heads; h += PREP_THREADS) gate[(size_t)t * g.heads + h] = 1.f / (1.f + expf(-yg[h]));
+  const int slot = slot_mapping[t];
+  if (slot < 0) return;
+  const size_t crow = (size_t)slot * g.row();
+  for (int i = threadIdx.x; i < g.kv_rank; i += PREP_THREADS) st_any(cache, dtype, crow + i, ykv[i] * rs_kv * w_kv[i]);
+  const float* cs = cos_sin + (size_t)positions[t] * g.rot_dims;
+  for (int j = threadIdx.x; j < g.rot_dim; j += PREP_THREADS)
+    st_any(cache, dtype, crow + g.kv_rank + j, rotary_entry(ykr, j, g.rot_dims, cs));
+}
+
+__global__ void latent_q_rope_kernel(const float* __restrict__ q, LatentGeom g, const int32_t* __restrict__ positions,
+                                     const float* __restrict__ cos_sin, float* __restrict__ q_abs) {
+  griddep_launch();
+  griddep_wait();
+  const int t = blockIdx.x;
+  const float* cs = cos_sin + (size_t)positions[t] * g.rot_dims;
+  const int hd = g.dim + g.rot_dim, D = g.row();
+  for (int e = threadIdx.x; e < g.heads * g.rot_dim; e += blockDim.x) {
+    const int h = e / g.rot_dim, j = e % g.rot_dim;
+    const float* v = q + ((size_t)t * g.heads + h) * hd + g.dim;
+    q_abs[((size_t)t * g.heads + h) * D + g.kv_rank + j] = rotary_entry(v, j, g.rot_dims, cs);
+  }
+}
+
+// NACC * 32 >= kv_rank.  Dynamic shared memory: Ks [KV_BLOCK][ldk] + Qs [LATENT_PAIRS][D] floats.
+template <class CT, int NACC>
+__global__ void __launch_bounds__(LAT_THREADS)
+latent_attn_kernel(const float* __restrict__ q_abs, const CT* __restrict__ cache, const AttnSeq* __restrict__ seqs,
+                   const LatentTile* __restrict__ tiles, const int32_t* __restrict__ block_table, int bt_stride,
+                   float* __restrict__ o_lat, LatentGeom g) {
+  extern __shared__ __align__(16) float smem_f[];
+  griddep_launch();
+  griddep_wait();
+  const int D = g.row(), R = g.kv_rank;
+  const int ldk = D | 1;  // odd row stride: lanes (= keys) hit 32 different banks in the score loop
+  float* Ks = smem_f;
+  float* Qs = smem_f + (size_t)KV_BLOCK * ldk;
+  const LatentTile tile = tiles[blockIdx.x];
+  const AttnSeq sq = seqs[tile.seq];
+  const int h0 = blockIdx.y * LATENT_PAIRS;
+  const int nh = min(g.heads - h0, LATENT_PAIRS);
+  const int npairs = tile.nq * nh;  // <= LATENT_PAIRS by construction of the tiles
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int pos0 = sq.kv_len - sq.q_len + tile.q0;  // position of the tile's first query
+  const int row0 = sq.q_start + tile.q0;            // its row in the step's flat token batch
+  for (int e = threadIdx.x; e < npairs * D; e += LAT_THREADS) {
+    const int p = e / D, d = e % D;
+    const int tq = p / nh, h = h0 + p % nh;
+    Qs[(size_t)p * D + d] = q_abs[((size_t)(row0 + tq) * g.heads + h) * D + d] * g.scale;
+  }
+  // this warp's two pairs
+  int pp[2], posq[2];
+  bool on[2];
+#pragma unroll
+  for (int u = 0; u < 2; ++u) {
+    pp[u] = warp + u * LAT_WARPS;
+    on[u] = pp[u] < npairs;
+    posq[u] = on[u] ? pos0 + pp[u] / nh : -1;
+  }
+  float m[2] = {-FLT_MAX, -FLT_MAX}, l[2] = {0.f, 0.f};
+  float acc[2][NACC];
+#pragma unroll
+  for (int u = 0; u < 2; ++u)
+#pragma unroll
+    for (int i = 0; i < NACC; ++i) acc[u][i] = 0.f;
+
+  const int pos_last = pos0 + tile.nq - 1;
+  const int kmin = g.window > 0 ? max(0, pos0 - g.window + 1) : 0;
+  const int32_t* bt = block_table + (size_t)sq.block_row * bt_stride;
+  for (int blk = kmin / KV_BLOCK; blk <= pos_last / KV_BLOCK; ++blk) {
+    __syncthreads();  // the previous block's rows (and, first time round, Qs) are settled
+    const CT* src = cache + (size_t)bt[blk] * KV_BLOCK * D;
+    for (int e = threadIdx.x; e < KV_BLOCK * D; e += LAT_THREADS) Ks[(size_t)(e / D) * ldk + e % D] = widen<CT>(src[e]);
+    __syncthreads();
+    const int kp = blk * KV_BLOCK + lane;  // this lane's key position
+    float s[2] = {0.f, 0.f};
+    const float* krow = Ks + (size_t)lane * ldk;
+    const float* q0p = Qs + (size_t)(on[0] ? pp[0] : 0) * D;
+    const float* q1p = Qs + (size_t)(on[1] ? pp[1] : 0) * D;
+    for (int d = 0; d < D; ++d) {
+      const float kv = krow[d];
+      s[0] = fmaf(q0p[d], kv, s[0]);
+      s[1] = fmaf(q1p[d], kv, s[1]);
+    }
+    float p[2];
+#pragma unroll
+    for (int u = 0; u < 2; ++u) {
+      const bool vis = on[u] && kp <= posq[u] && (g.window <= 0 || posq[u] - kp < g.window);
+      const float sv = vis ? s[u] : -FLT_MAX;
+      const float m_new = fmaxf(m[u], warp_max_f(sv));
+      // nothing visible so far (m_new still the sentinel): all weights 0, state unchanged
+      const float corr = m_new == -FLT_MAX ? 1.f : expf(m[u] - m_new);
+      p[u] = vis ? expf(sv - m_new) : 0.f;
+      l[u] = l[u] * corr + warp_sum_f(p[u]);
+      m[u] = m_new;
+#pragma unroll
+      for (int i = 0; i < NACC; ++i) acc[u][i] *= corr;
+    }
+    for (int j = 0; j < KV_BLOCK; ++j) {
+      const float p0 = __shfl_sync(0xffffffffu, p[0], j), p1 = __shfl_sync(0xffffffffu, p[1], j);
+      if (p0 == 0.f && p1 == 0.f) continue;  // warp-uniform
+      const float* cj = Ks + (size_t)j * ldk;
+#pragma unroll
+      for (int i = 0; i < NACC; ++i) {
+        const int d = lane + 32 * i;
+        if (d < R) {
+          const float cv = cj[d];
+          acc[0][i] = fmaf(p0, cv, acc[0][i]);
+          acc[1][i] = fmaf(p1, cv, acc[1][i]);
+        }
+      }
+    }
+  }
+#pragma unroll
+  for (int u = 0; u < 2; ++u) {
+    if (!on[u]) continue;
+    const int tq = pp[u] / nh, h = h0 + pp[u] % nh;
+    float* o = o_lat + ((size_t)(row0 + tq) * g.heads + h) * R;
+    const float inv = 1.f / l[u];
+#pragma unroll
+    for (int i = 0; i < NACC; ++i) {
+      const int d = lane + 32 * i;
+      if (d < R) o[d] = acc[u][i] * inv;
+    }
+  }
+}
+
+template <class CT, int NACC>
+cudaError_t launch_attn(const float* q_abs, const void* cache, const AttnSeq* seqs, const LatentTile* tiles, int n_tiles,
+                        const int32_t* block_table, int bt_stride, float* o_lat, const LatentGeom& g, cudaStream_t stream) {
+  const int D = g.row();
+  const size_t smem = ((size_t)KV_BLOCK * (D | 1) + (size_t)LATENT_PAIRS * D) * sizeof(float);
+  if (smem > 200 * 1024) return cudaErrorInvalidValue;
+  static size_t attr_bytes = 0;  // per instantiation
+  if (smem > 48 * 1024 && smem > attr_bytes) {
+    const cudaError_t e = cudaFuncSetAttribute(latent_attn_kernel<CT, NACC>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                               (int)smem);
+    if (e != cudaSuccess) return e;
+    attr_bytes = smem;
+  }
+  const dim3 grid(n_tiles, (g.heads + LATENT_PAIRS - 1) / LATENT_PAIRS);
+  return launch_k(latent_attn_kernel<CT, NACC>, grid, dim3(LAT_THREADS), smem, stream, q_abs,
+                  reinterpret_cast<const CT*>(cache), seqs, tiles, block_table, bt_stride, o_lat, g);
+}
+
+template <class CT>
+cudaError_t launch_attn_ct(const float* q_abs, const void* cache, const AttnSeq* seqs, const LatentTile* tiles, int n_tiles,
+                           const int32_t* block_table, int bt_stride, float* o_lat, const LatentGeom& g,
+                           cudaStream_t stream) {
+  if (g.kv_rank <= 128) return launch_attn<CT, 4>(q_abs, cache, seqs, tiles, n_tiles, block_table, bt_stride, o_lat, g, stream);
+  if (g.kv_rank <= 256) return launch_attn<CT, 8>(q_abs, cache, seqs, tiles, n_tiles, block_table, bt_stride, o_lat, g, stream);
+  if (g.kv_rank <= 512) return launch_attn<CT, 16>(q_abs, cache, seqs, tiles, n_tiles, block_table, bt_stride, o_lat, g, stream);
+  return cudaErrorInvalidValue;
+}
+
+}  // namespace
+
+cudaError_t latent_prep_launch(const float* y, int ldy, const LatentGeom& g, const float* w_q, const float* w_kv, float eps,
+                               const int32_t* positions, const int32_t* slot_mapping, const float* cos_sin, void* cq,
+                               void* cache, int dtype, float* gate, int T, cudaStream_t stream) {
+  if (T <= 0) return cudaSuccess;
+  if (g.rot_dims > g.rot_dim || (g.rot_dims & 1)) return cudaErrorInvalidValue;
+  return launch_k(latent_prep_kernel, dim3(T), dim3(PREP_THREADS), 0, stream, y, ldy, g, w_q, w_kv, eps, positions,
+                  slot_mapping, cos_sin, cq, cache, dtype, gate);
+}
+
+cudaError_t latent_q_rope_launch(const float* q, const LatentGeom& g, const int32_t* positions, const float* cos_sin,
+                                 float* q_abs, int T, cudaStream_t stream) {
+  if (T <= 0) return cudaSuccess;
+  return launch_k(latent_q_rope_kernel, dim3(T), dim3(128), 0, stream, q, g, positions, cos_sin, q_abs);
+}
+
+cudaError_t latent_attn_launch(const float* q_abs, const void* cache, int dtype, const AttnSeq* seqs,
+                               const LatentTile* tiles, int n_tiles, const int32_t* block_table, int bt_stride,
+                               float* o_lat, const LatentGeom& g, cudaStream_t stream) {
+  if (n_tiles <= 0) return cudaSuccess;
+  if (dtype == DT_BF16)
+    return launch_attn_ct<__nv_bfloat16>(q_abs, cache, seqs, tiles, n_tiles, block_table, bt_stride, o_lat, g, stream);
+  return launch_attn_ct<float>(q_abs, cache, seqs, tiles, n_tiles, block_table, bt_stride, o_lat, g, stream);
+}
+
+}  // namespace tgis

@@ -629,4 +629,126 @@ cudaError_t rope_kvwrite_launch(__nv_bfloat16* qkv, const int32_t* positions, co
                   n_q, n_kv);
 }
 
+// ------------------------------------------------------------------------------------------------ fp32 residual stream
+// Models that keep the residual sum and every norm in fp32: rows of any width (scalar, coalesced; the row is parked in
+// shared memory between its passes).  Outputs that feed a matrix product are written in the product's operand type.
+__device__ __forceinline__ void st_dt(void* out, int dt, size_t i, float v) {
+  if (dt == DT_BF16) reinterpret_cast<__nv_bfloat16*>(out)[i] = __float2bfloat16_rn(v);
+  else reinterpret_cast<float*>(out)[i] = v;
+}
+__device__ __forceinline__ float ld_dt(const void* in, int dt, size_t i) {
+  return dt == DT_BF16 ? __bfloat162float(reinterpret_cast<const __nv_bfloat16*>(in)[i]) : reinterpret_cast<const float*>(in)[i];
+}
+
+__global__ void __launch_bounds__(NORM_THREADS)
+rmsnorm_f32_kernel(const float* __restrict__ x, int ldx, const float* __restrict__ w, float w_off, void* __restrict__ out,
+                   int out_dtype, int ldo, int n, float eps) {
+  __shared__ float red[NORM_THREADS / 32];
+  griddep_launch();
+  griddep_wait();
+  const float* xr = x + (size_t)blockIdx.x * ldx;
+  float ss = 0.f;
+  for (int i = threadIdx.x; i < n; i += NORM_THREADS) ss += xr[i] * xr[i];
+  const float rs = 1.f / sqrtf(block_sum<NORM_THREADS>(ss, red) / (float)n + eps);
+  for (int i = threadIdx.x; i < n; i += NORM_THREADS)
+    st_dt(out, out_dtype, (size_t)blockIdx.x * ldo + i, xr[i] * rs * (w_off + (w ? w[i] : 0.f)));
+}
+cudaError_t rmsnorm_f32_launch(const float* x, int ldx, const float* w, float w_off, void* out, int out_dtype, int ldo, int T,
+                               int n, float eps, cudaStream_t stream) {
+  if (T <= 0) return cudaSuccess;
+  return launch_k(rmsnorm_f32_kernel, dim3(T), dim3(NORM_THREADS), 0, stream, x, ldx, w, w_off, out, out_dtype, ldo, n, eps);
+}
+
+__global__ void embed_scale_f32_kernel(const int32_t* __restrict__ tok, const void* __restrict__ table, int table_dtype,
+                                       float scale, float* __restrict__ resid, int hidden, int vocab) {
+  griddep_launch();
+  griddep_wait();
+  int row = tok[blockIdx.x];
+  if (row < 0 || row >= vocab) row = 0;
+  for (int i = threadIdx.x; i < hidden; i += blockDim.x)
+    resid[(size_t)blockIdx.x * hidden + i] = ld_dt(table, table_dtype, (size_t)row * hidden + i) * scale;
+}
+cudaError_t embed_scale_f32_launch(const int32_t* token_ids, const void* table, int table_dtype, float scale, float* resid,
+                                   int T, int hidden, int vocab, cudaStream_t stream) {
+  if (T <= 0) return cudaSuccess;
+  return launch_k(embed_scale_f32_kernel, dim3(T), dim3(128), 0, stream, token_ids, table, table_dtype, scale, resid, hidden,
+                  vocab);
+}
+
+__global__ void __launch_bounds__(NORM_THREADS) resid_tail_kernel(ResidTail a, int hidden) {
+  extern __shared__ float row_buf[];
+  __shared__ float red[NORM_THREADS / 32];
+  griddep_launch();
+  griddep_wait();
+  const int t = blockIdx.x;
+  const size_t base = (size_t)t * hidden;
+  float ss = 0.f;
+  for (int i = threadIdx.x; i < hidden; i += NORM_THREADS) {
+    float y = 0.f;
+    if (a.y_main != nullptr) {
+      y = a.y_main[base + i];
+    } else {
+      if (a.y_rows != nullptr)
+        for (int k = 0; k < a.top; ++k)
+          y = fmaf(a.mix_w[(size_t)t * a.top + k], a.y_rows[(size_t)a.inv[(size_t)t * a.top + k] * hidden + i], y);
+      if (a.y_side != nullptr) y = fmaf(a.side_gate != nullptr ? a.side_gate[t] : 1.f, a.y_side[base + i], y);
+    }
+    row_buf[i] = y;
+    ss += y * y;
+  }
+  const float rs = 1.f / sqrtf(block_sum<NORM_THREADS>(ss, red) / (float)hidden + a.eps);
+  float ss2 = 0.f;
+  for (int i = threadIdx.x; i < hidden; i += NORM_THREADS) {
+    const float r = a.resid[base + i] + a.mult * (row_buf[i] * rs * (a.w_off + a.w_post[i]));
+    a.resid[base + i] = r;
+    row_buf[i] = r;
+    ss2 += r * r;
+  }
+  if (a.w_pre == nullptr) return;
+  const float rs2 = 1.f / sqrtf(block_sum<NORM_THREADS>(ss2, red) / (float)hidden + a.eps);
+  for (int i = threadIdx.x; i < hidden; i += NORM_THREADS)
+    st_dt(a.out, a.out_dtype, base + i, row_buf[i] * rs2 * (a.w_off + a.w_pre[i]));
+}
+cudaError_t resid_tail_launch(const ResidTail& a, int T, int hidden, cudaStream_t stream) {
+  if (T <= 0) return cudaSuccess;
+  if (a.w_post == nullptr || a.resid == nullptr || (size_t)hidden * 4 > 48 * 1024) return cudaErrorInvalidValue;
+  return launch_k(resid_tail_kernel, dim3(T), dim3(NORM_THREADS), (size_t)hidden * sizeof(float), stream, a, hidden);
+}
+
+__global__ void gather_rows_any_kernel(const int32_t* __restrict__ idx, const uint8_t* __restrict__ x,
+                                       uint8_t* __restrict__ out, int row_bytes) {
+  griddep_launch();
+  griddep_wait();
+  const uint8_t* src = x + (size_t)idx[blockIdx.x] * row_bytes;
+  uint8_t* dst = out + (size_t)blockIdx.x * row_bytes;
+  if (row_bytes % 4 == 0)
+    for (int i = threadIdx.x; i < row_bytes / 4; i += blockDim.x)
+      reinterpret_cast<uint32_t*>(dst)[i] = reinterpret_cast<const uint32_t*>(src)[i];
+  else
+    for (int i = threadIdx.x; i < row_bytes; i += blockDim.x) dst[i] = src[i];
+}
+cudaError_t gather_rows_any_launch(const void* x, const int32_t* rows, void* out, int R, int hidden, int dtype,
+                                   cudaStream_t stream) {
+  if (R <= 0) return cudaSuccess;
+  return launch_k(gather_rows_any_kernel, dim3(R), dim3(128), 0, stream, rows, reinterpret_cast<const uint8_t*>(x),
+                  reinterpret_cast<uint8_t*>(out), (int)(hidden * dt_size(dtype)));
+}
+
+__global__ void weight_place_kernel(const __nv_bfloat16* __restrict__ src, int rows, int cols, void* __restrict__ dst,
+                                    int dst_dtype, long long rs, long long cs) {
+  const size_t total = (size_t)rows * cols;
+  for (size_t e = blockIdx.x * (size_t)blockDim.x + threadIdx.x; e < total; e += (size_t)gridDim.x * blockDim.x) {
+    const size_t r = e / cols, c = e % cols;
+    st_dt(dst, dst_dtype, (size_t)(r * rs + c * cs), __bfloat162float(src[e]));
+  }
+}
+cudaError_t weight_place_launch(const __nv_bfloat16* src, int rows, int cols, void* dst, int dst_dtype, long long rs,
+                                long long cs, cudaStream_t stream) {
+  if (rows <= 0 || cols <= 0) return cudaSuccess;
+  const size_t total = (size_t)rows * cols;
+  const int blocks = (int)std::min<size_t>((total + 255) / 256, 148 * 8);
+  weight_place_kernel<<<blocks, 256, 0, stream>>>(src, rows, cols, dst, dst_dtype, rs, cs);
+  return cudaGetLastError();
+}
+
 }  // namespace tgis

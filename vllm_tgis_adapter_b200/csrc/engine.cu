@@ -234,6 +234,37 @@ struct tgis_engine {
   std::set<std::string> opt_loaded;  // tensor names seen by load_weight_opt (completeness check at start)
   std::vector<LayerW> layers;
   CUtensorMap m_lm{};
+  // ---- layer-list architectures (TGIS_ARCH_PONENEX): per-layer geometry, weights, caches and the fp32-residual buffers
+  bool pnx_on = false;
+  tgis_model_spec pnx_spec{};
+  std::vector<tgis_layer_spec> pnx_layer_specs;
+  struct PnxLayer {
+    tgis_layer_spec sp{};
+    LatentGeom g{};
+    void *w_down = nullptr, *w_uq = nullptr, *w_ukT = nullptr, *w_uv = nullptr, *w_o = nullptr;   // operand type
+    float *norm1 = nullptr, *norm1b = nullptr, *norm2 = nullptr, *norm2b = nullptr, *qnorm = nullptr, *kvnorm = nullptr;
+    const float* cos_sin = nullptr;  // [max_model_len][rot_dims]
+    void* cache = nullptr;           // [num_blocks][KV_BLOCK][kv_rank + rot_dim], operand type
+    void *w_router = nullptr, *w_gu_e = nullptr, *w_d_e = nullptr, *w_gu_s = nullptr, *w_d_s = nullptr;
+    float* router_b = nullptr;
+    int n_down() const { return sp.q_rank + sp.kv_rank + sp.rot_dim + sp.heads; }
+  };
+  std::vector<PnxLayer> pnx_layers;
+  std::vector<void*> pnx_allocs;                     // everything pnx_alloc handed out
+  std::vector<std::pair<std::pair<float, int>, float*>> pnx_rope_tables;  // (base, dims) -> table
+  std::set<std::string> pnx_loaded;
+  size_t pnx_expected_tensors = 0;
+  int pnx_dt = DT_BF16;                              // operand type of weights / matrix-product inputs / cache rows
+  void *pnx_embed = nullptr, *pnx_head = nullptr, *pnx_hA = nullptr, *pnx_cq = nullptr, *pnx_oA = nullptr, *pnx_actS = nullptr,
+       *pnx_actE = nullptr, *pnx_last = nullptr;
+  float *pnx_final_norm = nullptr, *pnx_resid = nullptr, *pnx_y1 = nullptr, *pnx_gate = nullptr, *pnx_q = nullptr,
+        *pnx_qabs = nullptr, *pnx_olat = nullptr, *pnx_o = nullptr, *pnx_rl = nullptr, *pnx_mixw = nullptr, *pnx_sgate = nullptr,
+        *pnx_yS = nullptr, *pnx_yE = nullptr;
+  int32_t *pnx_ids = nullptr, *pnx_segoff = nullptr, *pnx_order = nullptr, *pnx_inv = nullptr;
+  int pnx_tile_tokens = 1, step_n_ltiles = 0;
+  size_t off_ltiles = 0;
+  int logit_rows_cap = 0;                            // rows of the logits buffer (>= max_num_seqs)
+  std::string pnx_dump_path;                         // TGIS_DUMP_RESID: append the residual stream after every layer (debug)
   // kv cache
   DevBuf<bf16> k_cache, v_cache;
   size_t kv_layer_elems = 0;
@@ -275,6 +306,7 @@ struct tgis_engine {
   DevBuf<SampleOut> d_samp_out;
   SampleOut* h_samp_out = nullptr;
   SampleOut* h_plp_out = nullptr;  // prompt-logprob pass results (kept apart from the step's sampled rows)
+  float* h_trace_logits = nullptr; // pinned landing area of the trace replay's logits (logit_rows_cap rows)
   // staging
   uint8_t* h_stage = nullptr;
   DevBuf<uint8_t> d_stage;
@@ -382,10 +414,12 @@ struct tgis_engine {
         fprintf(stderr, "  %5.0f %5.0f %6.0f %5.0f\n", host_phases[i].sched, host_phases[i].launch, host_phases[i].wait,
                 host_phases[i].post);
     }
+    for (void* q : pnx_allocs) cudaFree(q);
     if (h_stage) cudaFreeHost(h_stage);
     if (h_samp_out) cudaFreeHost(h_samp_out);
     if (h_allow) cudaFreeHost(h_allow);
     if (h_plp_out) cudaFreeHost(h_plp_out);
+    if (h_trace_logits) cudaFreeHost(h_trace_logits);
     if (shm) {
       if (rank == 0) shm->shutdown.store(1, std::memory_order_release);
       munmap(shm, shm_bytes);
@@ -425,6 +459,8 @@ struct tgis_engine {
     Fl = c.ffn / tp;
     Vl = c.vocab / tp;
     opt = c.arch == TGIS_ARCH_OPT;
+    pnx_on = c.arch == TGIS_ARCH_PONENEX;
+    if (pnx_on) logits_bf16 = false;  // fp32 logits straight from the accumulators
     model_head_dim = opt ? c.head_dim : HEAD_DIM;
     attn_scale = 1.0f / std::sqrt((float)model_head_dim);  // zero-padded head dims add nothing to q . k
     pos_rows = opt ? c.max_model_len + 2 : 0;
@@ -458,10 +494,13 @@ struct tgis_engine {
       const std::string v = e;
       tp_exchange_force = v == "nccl" ? 0 : v == "oneshot" ? 1 : v == "twoshot" ? 2 : -1;
     }
+    if (pnx_on) logits_bf16 = false;
     lsz = logits_bf16 ? 2 : 4;
+    logit_rows_cap = std::max(S_max, 64);
 
-    // ---- weights: one arena
     const size_t H = c.hidden, F = Fl, V = c.vocab, L = c.n_layers;  // F: this rank's ffn shard
+    if (!pnx_on) {
+    // ---- weights: one arena
     const size_t per_layer = (size_t)qkv_dim * H + H * q_dim + 2 * F * H + H * F + 2 * H;
     const size_t opt_extra = opt ? (size_t)pos_rows * H + H + L * ((size_t)qkv_dim + 4 * H + F) + 64 * (6 * L + 4) : 0;
     const size_t total = V * H /*embed*/ + V * H /*lm_head*/ + H /*norm*/ + (size_t)c.max_model_len * HEAD_DIM +
@@ -537,23 +576,25 @@ struct tgis_engine {
       lora_v.alloc(T_alloc * 3 * R);
       gu_buf.alloc(T_alloc * (size_t)2 * F);
     }
+    }  // !pnx_on
     last_hidden.alloc(S_alloc * H);
-    logits.alloc((size_t)S_max * V * lsz);
+    logits.alloc((size_t)logit_rows_cap * V * lsz);
     if (tp > 1) {
       logits_shard.alloc((size_t)S_max * Vl * lsz);
       logits_gather.alloc((size_t)tp * S_max * Vl * lsz);
     }
-    xn.zero(); attn_out.zero(); act.zero(); last_hidden.zero();
+    if (!pnx_on) { xn.zero(); attn_out.zero(); act.zero(); }
+    last_hidden.zero();
     gemm_ws.alloc(gemm_workspace_bytes(num_sms) / sizeof(float));
     gemm_counters.alloc(1 << 16);
     gemm_counters.zero();
     attn_arrive.alloc((size_t)S_max * std::max(nkv, 1));
     attn_arrive.zero();
     norm_ssq.alloc((size_t)2 * GEMM_NORM_MAX_T * (c.hidden / 128 + 1));
-    const int G = c.n_q_heads / c.n_kv_heads;
+    const int G = c.n_q_heads / std::max(c.n_kv_heads, 1);
     part_o.alloc((size_t)S_max * nkv * max_splits_cap * G * HEAD_DIM);
     part_ml.alloc((size_t)S_max * nkv * max_splits_cap * G * 2);
-    samp_scratch.alloc((size_t)S_max * V);
+    samp_scratch.alloc((size_t)logit_rows_cap * V);
     seen_bitmap.alloc((size_t)S_max * bitmap_words);
     seen_bitmap.zero();
     if (rank == 0) {  // only the sampling rank needs the masks
@@ -563,6 +604,7 @@ struct tgis_engine {
     d_samp_out.alloc(S_max);
     CK(cudaHostAlloc(&h_samp_out, sizeof(SampleOut) * S_max, cudaHostAllocDefault));
     CK(cudaHostAlloc(&h_plp_out, sizeof(SampleOut) * S_max, cudaHostAllocDefault));
+    CK(cudaHostAlloc(&h_trace_logits, (size_t)logit_rows_cap * V * sizeof(float), cudaHostAllocDefault));
 
     // ---- staging layout
     size_t o = 0;
@@ -580,10 +622,11 @@ struct tgis_engine {
     off_decids = place(4 * (size_t)S_max);
     off_tileseq = place(4 * (size_t)tiles_max);
     off_tileq0 = place(4 * (size_t)tiles_max);
-    off_samplesrc = place(4 * (size_t)S_max);
+    off_samplesrc = place(4 * (size_t)std::max(S_max, logit_rows_cap));
     off_rows = place(sizeof(SampleRow) * (size_t)S_max);
     off_epoch = place(4 * sizeof(uint32_t));  // tensor parallelism: exchange epochs before this step ([0], [1]: per
                                                // parity) and the logits-gather epoch ([2])
+    off_ltiles = place(sizeof(LatentTile) * (size_t)(T_max + S_max));  // latent-attention query tiles (TGIS_ARCH_PONENEX)
     off_bt = place(4 * (size_t)S_max * bt_stride);
     // decode work items follow the USED part of the block table (items_off(S)); room for the worst case
     place(sizeof(DecItem) * (1 + (size_t)S_max * max_splits_cap));
@@ -593,6 +636,15 @@ struct tgis_engine {
     d_stage.alloc(stage_bytes);
     d_stage.zero();
 
+    if (pnx_on) {
+      init_pnx();
+      free_slots.resize(S_max);
+      for (int i = 0; i < S_max; ++i) free_slots[i] = S_max - 1 - i;
+      snapshot();
+      CK(cudaDeviceSynchronize());
+      ready = true;
+      return;
+    }
     // ---- tensor maps (weights: box 128 rows x 64 k; activations: box BT rows x 64 k)
     auto wmap = [&](CUtensorMap* m, const bf16* w, size_t rows, size_t cols) {
       if (make_tmap_bf16_2d(m, w, rows, cols, cols, 128, 64) != 0) throw CudaError("cuTensorMapEncodeTiled(weight) failed");
@@ -917,6 +969,7 @@ struct tgis_engine {
 
   int load_weight(const std::string& name, const void* ptr, int64_t rows, int64_t cols) {
     if (opt) return load_weight_opt(name, ptr, rows, cols);
+    if (pnx_on) return pnx_load_weight(name, ptr, rows, cols);
     const tgis_config& c = cfg;
     const int64_t H = c.hidden, F = c.ffn, V = c.vocab;
     const uint8_t* src = static_cast<const uint8_t*>(ptr);
@@ -1049,6 +1102,12 @@ struct tgis_engine {
   }
 
   void finalize_weights() {
+    if (pnx_on) {  // a checkpoint with a tensor missing must not come up on zeros
+      if (pnx_loaded.size() != pnx_expected_tensors)
+        throw CudaError("checkpoint incomplete: " + std::to_string(pnx_loaded.size()) + " of " +
+                        std::to_string(pnx_expected_tensors) + " tensors loaded");
+      return;
+    }
     if (opt) {
       // an OPT checkpoint with a tensor missing must not come up healthy on zeros (the reference's engine fails the load)
       const size_t expected = 4 + (size_t)16 * cfg.n_layers;
@@ -1059,6 +1118,324 @@ struct tgis_engine {
     if (!lm_head_loaded)  // tie_word_embeddings
       CK(cudaMemcpy(lm_head, embed + (size_t)rank * Vl * cfg.hidden, (size_t)Vl * cfg.hidden * sizeof(bf16),
                     cudaMemcpyDeviceToDevice));
+  }
+
+  // ------------------------------------------------------------------------------------------------ layer-list models
+  // TGIS_ARCH_PONENEX.  Scheduler, sequence slots, block manager, step metadata, lm_head rows, sampler and CUDA-graph
+  // replay are the engine's; what differs is the layer stack (pnx_forward) and the per-layer cache of latent rows, which
+  // is paged with the same block ids as every other model's KV cache.
+  template <class T>
+  T* pnx_alloc(size_t count, bool zero = false) {
+    void* q = nullptr;
+    CK(cudaMalloc(&q, std::max<size_t>(count, 1) * sizeof(T)));
+    if (zero) CK(cudaMemset(q, 0, std::max<size_t>(count, 1) * sizeof(T)));
+    pnx_allocs.push_back(q);
+    return reinterpret_cast<T*>(q);
+  }
+  void* pnx_alloc_dt(size_t count, bool zero = false) {
+    return pnx_alloc<uint8_t>(count * dt_size(pnx_dt), zero);
+  }
+  // cos | sin of p * base^(-2i / dims), i < dims / 2, evaluated in double and stored fp32: [max_model_len][dims]
+  const float* pnx_rope_table(float base, int dims) {
+    for (auto& kv : pnx_rope_tables)
+      if (kv.first.first == base && kv.first.second == dims) return kv.second;
+    const int half = dims / 2;
+    std::vector<float> tab((size_t)cfg.max_model_len * std::max(dims, 1));
+    for (int pos = 0; pos < cfg.max_model_len; ++pos)
+      for (int i = 0; i < half; ++i) {
+        const double a = (double)pos * std::pow((double)base, -2.0 * i / dims);
+        tab[(size_t)pos * dims + i] = (float)std::cos(a);
+        tab[(size_t)pos * dims + half + i] = (float)std::sin(a);
+      }
+    float* d = pnx_alloc<float>(tab.size());
+    CK(cudaMemcpy(d, tab.data(), tab.size() * sizeof(float), cudaMemcpyHostToDevice));
+    pnx_rope_tables.push_back({{base, dims}, d});
+    return d;
+  }
+
+  void init_pnx() {
+    const tgis_config& c = cfg;
+    const size_t W = c.hidden, V = c.vocab, T = std::max(T_max, 16);
+    pnx_dt = pnx_spec.dtype == TGIS_DTYPE_F32 ? DT_F32 : DT_BF16;
+    if (const char* e = getenv("TGIS_DUMP_RESID")) pnx_dump_path = e;
+    pnx_embed = pnx_alloc_dt(V * W);
+    pnx_head = pnx_alloc_dt(V * W);
+    pnx_final_norm = pnx_alloc<float>(W);
+    pnx_expected_tensors = 3;
+    size_t m_down = 1, m_qr = 1, m_q = 1, m_qabs = 1, m_olat = 1, m_ov = 1, m_heads = 1, m_E = 1, m_top = 1, m_ff = 1, m_ffs = 1;
+    size_t cache_row_bytes = 0;
+    pnx_tile_tokens = LATENT_PAIRS;
+    pnx_layers.resize(pnx_layer_specs.size());
+    for (size_t i = 0; i < pnx_layers.size(); ++i) {
+      PnxLayer& l = pnx_layers[i];
+      const tgis_layer_spec& s = pnx_layer_specs[i];
+      l.sp = s;
+      l.g = LatentGeom{s.heads, s.dim, s.rot_dim, s.vdim, s.kv_rank, s.q_rank, s.window, s.rot_dims, s.scale};
+      const size_t hd = (size_t)s.dim + s.rot_dim, row = (size_t)s.kv_rank + s.rot_dim;
+      l.w_down = pnx_alloc_dt((size_t)l.n_down() * W);
+      l.w_uq = pnx_alloc_dt((size_t)s.heads * hd * s.q_rank);
+      l.w_ukT = pnx_alloc_dt((size_t)s.heads * s.kv_rank * s.dim);
+      l.w_uv = pnx_alloc_dt((size_t)s.heads * s.vdim * s.kv_rank);
+      l.w_o = pnx_alloc_dt(W * s.heads * s.vdim);
+      l.norm1 = pnx_alloc<float>(W);
+      l.norm1b = pnx_alloc<float>(W);
+      l.qnorm = pnx_alloc<float>(s.q_rank);
+      l.kvnorm = pnx_alloc<float>(s.kv_rank);
+      l.cos_sin = pnx_rope_table(s.rot_base, s.rot_dims);
+      pnx_expected_tensors += 11;  // norm1, norm1b, dq, dq.norm, uq, dkv, dkv.norm, uk, uv, g, o
+      if (s.mlp == TGIS_MLP_MOE) {
+        const size_t E = s.experts, ff = s.expert_ff, ffs = s.shared_ff;
+        l.norm2 = pnx_alloc<float>(W);
+        l.norm2b = pnx_alloc<float>(W);
+        l.w_router = pnx_alloc_dt((E + (ffs > 0 ? 1 : 0)) * W);
+        l.router_b = pnx_alloc<float>(E);
+        l.w_gu_e = pnx_alloc_dt(E * 2 * ff * W);
+        l.w_d_e = pnx_alloc_dt(E * W * ff);
+        pnx_expected_tensors += 4 + 3 * E;  // norm2, norm2b, router, router.b, e<j>.{gate, up, down}
+        if (ffs > 0) {
+          l.w_gu_s = pnx_alloc_dt(2 * ffs * W);
+          l.w_d_s = pnx_alloc_dt(W * ffs);
+          pnx_expected_tensors += 4;  // shared.{gate, up, down, sg}
+        }
+        m_E = std::max(m_E, E + 1); m_top = std::max<size_t>(m_top, s.top); m_ff = std::max(m_ff, ff); m_ffs = std::max(m_ffs, ffs);
+      }
+      m_down = std::max<size_t>(m_down, l.n_down()); m_qr = std::max<size_t>(m_qr, s.q_rank);
+      m_q = std::max(m_q, s.heads * hd); m_qabs = std::max(m_qabs, s.heads * row);
+      m_olat = std::max(m_olat, (size_t)s.heads * s.kv_rank); m_ov = std::max(m_ov, (size_t)s.heads * s.vdim);
+      m_heads = std::max<size_t>(m_heads, s.heads);
+      cache_row_bytes += row * dt_size(pnx_dt);
+      pnx_tile_tokens = std::min(pnx_tile_tokens, latent_tile_tokens(s.heads));
+    }
+    // activations
+    pnx_resid = pnx_alloc<float>(T * W);
+    pnx_hA = pnx_alloc_dt(T * W, true);
+    pnx_y1 = pnx_alloc<float>(T * m_down);
+    pnx_cq = pnx_alloc_dt(T * m_qr, true);
+    pnx_gate = pnx_alloc<float>(T * m_heads);
+    pnx_q = pnx_alloc<float>(T * m_q);
+    pnx_qabs = pnx_alloc<float>(T * m_qabs);
+    pnx_olat = pnx_alloc<float>(T * m_olat);
+    pnx_oA = pnx_alloc_dt(T * m_ov, true);
+    pnx_o = pnx_alloc<float>(T * W);
+    pnx_rl = pnx_alloc<float>(T * m_E);
+    pnx_mixw = pnx_alloc<float>(T * m_top);
+    pnx_sgate = pnx_alloc<float>(T);
+    pnx_ids = pnx_alloc<int32_t>(T * m_top);
+    pnx_order = pnx_alloc<int32_t>(T * m_top);
+    pnx_inv = pnx_alloc<int32_t>(T * m_top);
+    pnx_segoff = pnx_alloc<int32_t>(m_E + 1);
+    pnx_actS = pnx_alloc_dt(T * m_ffs, true);
+    pnx_yS = pnx_alloc<float>(T * W);
+    pnx_actE = pnx_alloc_dt(T * m_top * m_ff, true);
+    pnx_yE = pnx_alloc<float>(T * m_top * W);
+    pnx_last = pnx_alloc_dt((size_t)std::max(logit_rows_cap, 16) * W, true);
+    // paged cache of latent rows: the block ids of the engine's block manager index every layer's cache
+    size_t kv_bytes = c.kv_cache_bytes;
+    if (kv_bytes == 0) {
+      size_t free_b = 0, total_b = 0;
+      CK(cudaMemGetInfo(&free_b, &total_b));
+      kv_bytes = (size_t)(free_b * (double)(c.gpu_mem_fraction > 0 ? c.gpu_mem_fraction : 0.85f));
+    }
+    const size_t bytes_per_block = (size_t)KV_BLOCK * cache_row_bytes;
+    size_t nb = std::min(kv_bytes / std::max<size_t>(bytes_per_block, 1), (size_t)S_max * bt_stride + 1);
+    if (nb < 1) throw CudaError("cache too small for one block");
+    num_blocks = (int)nb;
+    for (PnxLayer& l : pnx_layers) l.cache = pnx_alloc_dt(nb * KV_BLOCK * l.g.row(), true);  // finite everywhere
+    free_blocks.resize(num_blocks);
+    for (int i = 0; i < num_blocks; ++i) free_blocks[i] = num_blocks - 1 - i;
+  }
+
+  int pnx_load_weight(const std::string& name, const void* ptr, int64_t rows, int64_t cols) {
+    const int64_t W = cfg.hidden, V = cfg.vocab;
+    const int64_t n = rows * cols;
+    // the checkpoint tensor (bf16, host or device) -> device scratch -> its place in the operand type
+    bf16* tmp_src = nullptr;
+    if (cudaMalloc(&tmp_src, (size_t)std::max<int64_t>(n, 1) * sizeof(bf16)) != cudaSuccess) return fail("cudaMalloc(scratch) failed");
+    struct Guard { bf16* p; ~Guard() { cudaFree(p); } } guard{tmp_src};
+    if (cudaMemcpy(tmp_src, ptr, (size_t)n * sizeof(bf16), cudaMemcpyDefault) != cudaSuccess) return fail("cudaMemcpy(weight) failed");
+    auto bad_shape = [&]() { return fail("shape mismatch for " + name + ": got " + std::to_string(rows) + "x" + std::to_string(cols)); };
+    // src viewed as [r, cc] -> dst[r * rs + c * cs]
+    auto place = [&](void* dst, int dt, int64_t r, int64_t cc, int64_t rs, int64_t cs) -> int {
+      if (r * cc != n) return bad_shape();
+      const cudaError_t e = weight_place_launch(tmp_src, (int)r, (int)cc, dst, dt, rs, cs, 0);
+      if (e != cudaSuccess || cudaDeviceSynchronize() != cudaSuccess) return fail("weight placement failed for " + name);
+      pnx_loaded.insert(name);
+      return 0;
+    };
+    auto at = [&](void* base, size_t elem_off) { return reinterpret_cast<uint8_t*>(base) + elem_off * dt_size(pnx_dt); };
+    auto mat = [&](void* dst, int64_t r, int64_t cc) { return place(dst, pnx_dt, r, cc, cc, 1); };
+    auto vec = [&](float* dst, int64_t len) { return place(dst, DT_F32, len, 1, 1, 1); };
+    if (name == "embed") return mat(pnx_embed, V, W);
+    if (name == "head") return mat(pnx_head, V, W);
+    if (name == "final.norm") return vec(pnx_final_norm, W);
+    if (name.size() < 3 || name[0] != 'l') return fail("unknown weight " + name);
+    const size_t dot = name.find('.');
+    if (dot == std::string::npos) return fail("unknown weight " + name);
+    const int li = atoi(name.substr(1, dot - 1).c_str());
+    if (li < 0 || li >= (int)pnx_layers.size()) return fail("layer index out of range in " + name);
+    PnxLayer& l = pnx_layers[li];
+    const tgis_layer_spec& s = l.sp;
+    const std::string sub = name.substr(dot + 1);
+    const int64_t hd = s.dim + s.rot_dim;
+    if (sub == "norm1") return vec(l.norm1, W);
+    if (sub == "norm1b") return vec(l.norm1b, W);
+    if (sub == "mix.dq") return mat(l.w_down, s.q_rank, W);
+    if (sub == "mix.dkv") return mat(at(l.w_down, (size_t)s.q_rank * W), s.kv_rank + s.rot_dim, W);
+    if (sub == "mix.g") return mat(at(l.w_down, (size_t)(s.q_rank + s.kv_rank + s.rot_dim) * W), s.heads, W);
+    if (sub == "mix.dq.norm") return vec(l.qnorm, s.q_rank);
+    if (sub == "mix.dkv.norm") return vec(l.kvnorm, s.kv_rank);
+    if (sub == "mix.uq") return mat(l.w_uq, s.heads * hd, s.q_rank);
+    if (sub == "mix.uk") {
+      // [heads * dim, kv_rank] -> per head the transpose [kv_rank, dim]: the matrix that folds W_uk into the query
+      if (n != (int64_t)s.heads * s.dim * s.kv_rank) return bad_shape();
+      for (int h = 0; h < s.heads; ++h) {
+        const cudaError_t e = weight_place_launch(tmp_src + (size_t)h * s.dim * s.kv_rank, s.dim, s.kv_rank,
+                                                  at(l.w_ukT, (size_t)h * s.kv_rank * s.dim), pnx_dt, 1, s.dim, 0);
+        if (e != cudaSuccess) return fail("weight placement failed for " + name);
+      }
+      if (cudaDeviceSynchronize() != cudaSuccess) return fail("weight placement failed for " + name);
+      pnx_loaded.insert(name);
+      return 0;
+    }
+    if (sub == "mix.uv") return mat(l.w_uv, (int64_t)s.heads * s.vdim, s.kv_rank);
+    if (sub == "mix.o") return mat(l.w_o, W, (int64_t)s.heads * s.vdim);
+    if (s.mlp != TGIS_MLP_MOE) return fail("unknown layer weight " + name);
+    const int64_t E = s.experts, ff = s.expert_ff, ffs = s.shared_ff;
+    if (sub == "norm2") return vec(l.norm2, W);
+    if (sub == "norm2b") return vec(l.norm2b, W);
+    if (sub == "mlp.router") return mat(l.w_router, E, W);
+    if (sub == "mlp.router.b") return vec(l.router_b, E);
+    if (ffs > 0) {
+      if (sub == "mlp.shared.sg") return mat(at(l.w_router, (size_t)E * W), 1, W);
+      // gate / up rows interleave (row 2j = gate_j, row 2j + 1 = up_j) so that one product's epilogue applies SwiGLU
+      if (sub == "mlp.shared.gate") return place(l.w_gu_s, pnx_dt, ffs, W, 2 * W, 1);
+      if (sub == "mlp.shared.up") return place(at(l.w_gu_s, (size_t)W), pnx_dt, ffs, W, 2 * W, 1);
+      if (sub == "mlp.shared.down") return mat(l.w_d_s, W, ffs);
+    }
+    if (sub.rfind("mlp.e", 0) == 0) {
+      const size_t d2 = sub.find('.', 5);
+      if (d2 == std::string::npos) return fail("unknown layer weight " + name);
+      const int ei = atoi(sub.substr(5, d2 - 5).c_str());
+      if (ei < 0 || ei >= E) return fail("expert index out of range in " + name);
+      const std::string which = sub.substr(d2 + 1);
+      if (which == "gate") return place(at(l.w_gu_e, (size_t)ei * 2 * ff * W), pnx_dt, ff, W, 2 * W, 1);
+      if (which == "up") return place(at(l.w_gu_e, (size_t)ei * 2 * ff * W + W), pnx_dt, ff, W, 2 * W, 1);
+      if (which == "down") return mat(at(l.w_d_e, (size_t)ei * W * ff), W, ff);
+    }
+    return fail("unknown layer weight " + name);
+  }
+
+  // Y = X W^T through the general kernel (dense)
+  void pnx_gemm(const void* X, int x_dt, int ldx, const void* Wt, void* Y, int y_dt, int ldy, int T, int N, int K,
+                int mode = GEMM_ANY_PLAIN) {
+    GemmAny a{};
+    a.X = X; a.W = Wt; a.Y = Y;
+    a.x_dtype = x_dt; a.w_dtype = pnx_dt; a.y_dtype = y_dt;
+    a.T = T; a.N = N; a.K = K; a.ldx = ldx; a.ldw = K; a.ldy = ldy;
+    a.batch = 1; a.mode = mode;
+    CK(gemm_any_launch(a, stream));
+    ++n_launches;
+  }
+
+  // embeddings + layer stack + final norm -> pnx_hA [T, hidden] (operand type), fp32 residual stream in pnx_resid
+  void pnx_forward(int T) {
+    const int W = cfg.hidden, A = pnx_dt;
+    const float eps = pnx_spec.norm_eps, mult = pnx_spec.residual_mult;
+    const int32_t* d_tok = ds<int32_t>(off_tok);
+    const int32_t* d_pos = ds<int32_t>(off_pos);
+    const int32_t* d_slot = ds<int32_t>(off_slotmap);
+    const AttnSeq* d_seqs = ds<AttnSeq>(off_seqs);
+    const int32_t* d_bt = ds<int32_t>(off_bt);
+    const LatentTile* d_tiles = ds<LatentTile>(off_ltiles);
+    CK(embed_scale_f32_launch(d_tok, pnx_embed, A, pnx_spec.embed_scale, pnx_resid, T, W, cfg.vocab, stream));
+    CK(rmsnorm_f32_launch(pnx_resid, W, pnx_layers[0].norm1, 1.f, pnx_hA, A, W, T, W, eps, stream));
+    n_launches += 2;
+    const int L = (int)pnx_layers.size();
+    for (int li = 0; li < L; ++li) {
+      PnxLayer& l = pnx_layers[li];
+      const tgis_layer_spec& s = l.sp;
+      const LatentGeom& g = l.g;
+      const int H = s.heads, hd = s.dim + s.rot_dim, D = g.row();
+      const float* next_pre = li + 1 < L ? pnx_layers[li + 1].norm1 : pnx_final_norm;
+      // ---- mixer: fused down-projections [q latent | kv latent | rotary key | gate logits]
+      pnx_gemm(pnx_hA, A, W, l.w_down, pnx_y1, DT_F32, l.n_down(), T, l.n_down(), W);
+      CK(latent_prep_launch(pnx_y1, l.n_down(), g, l.qnorm, l.kvnorm, eps, d_pos, d_slot, l.cos_sin, pnx_cq, l.cache, A,
+                            pnx_gate, T, stream));
+      pnx_gemm(pnx_cq, A, s.q_rank, l.w_uq, pnx_q, DT_F32, H * hd, T, H * hd, s.q_rank);
+      CK(latent_q_rope_launch(pnx_q, g, d_pos, l.cos_sin, pnx_qabs, T, stream));
+      {  // q_abs_h = W_uk,h^T q_nope_h  (one problem per head)
+        GemmAny a{};
+        a.X = pnx_q; a.W = l.w_ukT; a.Y = pnx_qabs;
+        a.x_dtype = DT_F32; a.w_dtype = A; a.y_dtype = DT_F32;
+        a.T = T; a.N = s.kv_rank; a.K = s.dim; a.ldx = H * hd; a.ldw = s.dim; a.ldy = H * D;
+        a.batch = H; a.x_bs = hd; a.w_bs = (long long)s.kv_rank * s.dim; a.y_bs = D;
+        CK(gemm_any_launch(a, stream));
+      }
+      CK(latent_attn_launch(pnx_qabs, l.cache, A, d_seqs, d_tiles, step_n_ltiles, d_bt, bt_stride, pnx_olat, g, stream));
+      {  // o_h = gate_h * W_uv,h o_lat_h
+        GemmAny a{};
+        a.X = pnx_olat; a.W = l.w_uv; a.Y = pnx_oA;
+        a.x_dtype = DT_F32; a.w_dtype = A; a.y_dtype = A;
+        a.T = T; a.N = s.vdim; a.K = s.kv_rank; a.ldx = H * s.kv_rank; a.ldw = s.kv_rank; a.ldy = H * s.vdim;
+        a.batch = H; a.x_bs = s.kv_rank; a.w_bs = (long long)s.vdim * s.kv_rank; a.y_bs = s.vdim;
+        a.mode = GEMM_ANY_ROWSCALE; a.row_scale = pnx_gate; a.scale_ld = H;
+        CK(gemm_any_launch(a, stream));
+      }
+      n_launches += 5;
+      pnx_gemm(pnx_oA, A, H * s.vdim, l.w_o, pnx_o, DT_F32, W, T, W, H * s.vdim);
+      const bool moe = s.mlp == TGIS_MLP_MOE;
+      {
+        ResidTail rt{};
+        rt.y_main = pnx_o; rt.w_post = l.norm1b; rt.w_pre = moe ? l.norm2 : next_pre;
+        rt.resid = pnx_resid; rt.out = pnx_hA; rt.out_dtype = A; rt.mult = mult; rt.w_off = 1.f; rt.eps = eps;
+        CK(resid_tail_launch(rt, T, W, stream));
+        ++n_launches;
+      }
+      if (moe) {
+        const int E = s.experts, top = s.top, ff = s.expert_ff, ffs = s.shared_ff;
+        const int n_rl = E + (ffs > 0 ? 1 : 0);
+        pnx_gemm(pnx_hA, A, W, l.w_router, pnx_rl, DT_F32, n_rl, T, n_rl, W);
+        CK(moe_route_launch(pnx_rl, n_rl, l.router_b, E, top, pnx_ids, pnx_mixw, ffs > 0 ? pnx_sgate : nullptr, T, stream));
+        CK(moe_align_launch(pnx_ids, T, top, E, pnx_segoff, pnx_order, pnx_inv, stream));
+        n_launches += 2;
+        if (ffs > 0) {
+          pnx_gemm(pnx_hA, A, W, l.w_gu_s, pnx_actS, A, ffs, T, 2 * ffs, W, GEMM_ANY_SWIGLU);
+          pnx_gemm(pnx_actS, A, ffs, l.w_d_s, pnx_yS, DT_F32, W, T, W, ffs);
+        }
+        {  // routed experts: one row segment per expert
+          GemmAny a{};
+          a.X = pnx_hA; a.W = l.w_gu_e; a.Y = pnx_actE;
+          a.x_dtype = A; a.w_dtype = A; a.y_dtype = A;
+          a.T = T * top; a.N = 2 * ff; a.K = W; a.ldx = W; a.ldw = W; a.ldy = ff;
+          a.batch = 1; a.seg_off = pnx_segoff; a.n_groups = E; a.w_gs = (long long)2 * ff * W;
+          a.gather = pnx_order; a.gather_div = top; a.mode = GEMM_ANY_SWIGLU;
+          CK(gemm_any_launch(a, stream));
+          GemmAny b{};
+          b.X = pnx_actE; b.W = l.w_d_e; b.Y = pnx_yE;
+          b.x_dtype = A; b.w_dtype = A; b.y_dtype = DT_F32;
+          b.T = T * top; b.N = W; b.K = ff; b.ldx = ff; b.ldw = ff; b.ldy = W;
+          b.batch = 1; b.seg_off = pnx_segoff; b.n_groups = E; b.w_gs = (long long)W * ff;
+          CK(gemm_any_launch(b, stream));
+          n_launches += 2;
+        }
+        ResidTail rt{};
+        rt.y_rows = pnx_yE; rt.inv = pnx_inv; rt.mix_w = pnx_mixw; rt.top = top;
+        rt.y_side = ffs > 0 ? pnx_yS : nullptr; rt.side_gate = ffs > 0 ? pnx_sgate : nullptr;
+        rt.w_post = l.norm2b; rt.w_pre = next_pre;
+        rt.resid = pnx_resid; rt.out = pnx_hA; rt.out_dtype = A; rt.mult = mult; rt.w_off = 1.f; rt.eps = eps;
+        CK(resid_tail_launch(rt, T, W, stream));
+        ++n_launches;
+      }
+      if (!pnx_dump_path.empty() && !capturing) {
+        CK(cudaStreamSynchronize(stream));
+        std::vector<float> hbuf((size_t)T * W);
+        CK(cudaMemcpy(hbuf.data(), pnx_resid, hbuf.size() * sizeof(float), cudaMemcpyDeviceToHost));
+        if (FILE* f = fopen(pnx_dump_path.c_str(), "ab")) {
+          fwrite(hbuf.data(), sizeof(float), hbuf.size(), f);
+          fclose(f);
+        }
+      }
+    }
   }
 
   // ------------------------------------------------------------------------------------------------ device step
@@ -1132,6 +1509,8 @@ struct tgis_engine {
     }
     if (opt) {
       opt_layers(T, n_dec, n_tiles, max_dec_kv, S, R);  // embeddings + layer stack + final LayerNorm -> xn
+    } else if (pnx_on) {
+      pnx_forward(T);  // embeddings + layer stack + final norm -> pnx_hA
     } else {
       CK(embed_gather_launch(d_tok, embed, resid.p, T, H, V, stream));
       ++n_launches;
@@ -1143,7 +1522,7 @@ struct tgis_engine {
     // T while the stand-alone kernel spreads over all SMs -- hence the token limit)
     // ... unless the qkv launch reduces its split tiles on chip (cluster mode): then the epilogue is spread over the
     // cluster's CTAs by token and the fusion pays up to 256 tokens (TGIS_FUSE_ROPE_CLUSTER_MAX_T)
-    const int qkv_cluster = cfg.debug_gemm_ref ? 0 : gemm_cluster_split(T, qkv_dim, H, num_sms);
+    const int qkv_cluster = (cfg.debug_gemm_ref || pnx_on) ? 0 : gemm_cluster_split(T, qkv_dim, H, num_sms);
     // LoRA steps: the adapter deltas are added to the RAW projections (before RoPE, before SwiGLU, before the residual
     // add), so the fused epilogues are switched off for the step and the deltas land between the GEMM and its consumer
     const bool lora = (samp_complex & 4) != 0 && max_loras > 0;
@@ -1155,18 +1534,18 @@ struct tgis_engine {
       n_launches += 2;
     };
     if (lora) ++lora_steps;
-    const bool rope_fused = !lora && fuse_rope && !cfg.debug_gemm_ref && gemm_even_split(T, qkv_dim, H, num_sms) >= 2 &&
+    const bool rope_fused = !pnx_on && !lora && fuse_rope && !cfg.debug_gemm_ref && gemm_even_split(T, qkv_dim, H, num_sms) >= 2 &&
                             T <= (qkv_cluster > 0 ? std::max(rope_fuse_max_t, rope_fuse_cluster_max_t) : rope_fuse_max_t);
     // residual add + RMSNorm inside the GEMMs either side of it (single GPU, small steps, both row-"producers" reduced
     // on chip): o-proj -> [post-attention norm] -> gate_up and down-proj -> [next layer's input norm] -> qkv
-    const bool norm_fused = !lora && fuse_norm && tp == 1 && !cfg.debug_gemm_ref && T <= GEMM_NORM_MAX_T && H % 128 == 0 && H / 128 <= GEMM_NORM_MAX_PARTS &&
+    const bool norm_fused = !pnx_on && !lora && fuse_norm && tp == 1 && !cfg.debug_gemm_ref && T <= GEMM_NORM_MAX_T && H % 128 == 0 && H / 128 <= GEMM_NORM_MAX_PARTS &&
                             gemm_cluster_split(T, H, q_dim, num_sms) > 0 && gemm_cluster_split(T, H, F, num_sms) > 0;
     const int n_parts = H / 128;
     float* ssq_attn = norm_ssq.p;                                      // written by o-proj, read by gate_up
     float* ssq_mlp = norm_ssq.p + (size_t)GEMM_NORM_MAX_T * n_parts;   // written by down-proj, read by the next qkv
     const GemmNorm prod_attn{resid.p, ssq_attn, nullptr, nullptr, nullptr, 0, 0.f};
     const GemmNorm prod_mlp{resid.p, ssq_mlp, nullptr, nullptr, nullptr, 0, 0.f};
-    for (int li = 0; li < (opt ? 0 : c.n_layers); ++li) {  // Llama stack (OPT: opt_layers() above)
+    for (int li = 0; li < ((opt || pnx_on) ? 0 : c.n_layers); ++li) {  // Llama stack (OPT: opt_layers() above)
       LayerW& l = layers[li];
       const GemmNorm cons_qkv{nullptr, nullptr, resid.p, ssq_mlp, l.ln1, n_parts, c.rms_eps};
       const GemmNorm cons_gu{nullptr, nullptr, resid.p, ssq_attn, l.ln2, n_parts, c.rms_eps};
@@ -1266,13 +1645,12 @@ struct tgis_engine {
     // every rank has finished READING this step's buffers before a faster rank overwrites them in the next step.
     if (ar_fused) fused_ar_norm(1, final_norm, T);
     if (R > 0) {
-      if (ar_fused || opt) {
+      if (ar_fused || opt || pnx_on) {
       } else {
         CK(add_rmsnorm_launch(tmp.p, resid.p, final_norm, xn.p, T, H, c.rms_eps, stream));
         ++n_launches;
       }
-      CK(gather_rows_launch(xn.p, ds<int32_t>(off_samplesrc), last_hidden.p, R, H, stream));
-      ++n_launches;
+      gather_final_rows(R);
       lm_head_logits(R, 1);
       if (rank == 0) {
         CK(sampler_launch(logits_ptr(), logits_bf16 ? 1 : 0, V, V, ds<SampleRow>(off_rows), R, seen_bitmap.p, bitmap_words,
@@ -1344,11 +1722,20 @@ struct tgis_engine {
   // lm_head over `rows` rows of last_hidden -> the full [rows, V] logits on rank 0 (logits_ptr()).  Tensor parallel: every
   // rank computes its vocabulary shard; with peer mappings the shards are pushed into rank 0's buffer (logits_push_kernel,
   // no NCCL in the step), otherwise ncclAllGather + re-layout.
+  // rows listed at off_samplesrc of the final-normed hidden states -> the lm_head's input rows
+  void gather_final_rows(int m) {
+    if (pnx_on) CK(gather_rows_any_launch(pnx_hA, ds<int32_t>(off_samplesrc), pnx_last, m, cfg.hidden, pnx_dt, stream));
+    else CK(gather_rows_launch(xn.p, ds<int32_t>(off_samplesrc), last_hidden.p, m, cfg.hidden, stream));
+    ++n_launches;
+  }
+
   void lm_head_logits(int rows, int lg_idx) {
     const tgis_config& c = cfg;
     const int H = c.hidden, V = c.vocab;
     const int lm_mode = logits_bf16 ? 0 : 1;
-    if (tp == 1) {
+    if (pnx_on) {
+      pnx_gemm(pnx_last, pnx_dt, H, pnx_head, logits.p, DT_F32, V, rows, V, H);
+    } else if (tp == 1) {
       gemm(xm_last, m_lm, last_hidden.p, lm_head, logits.p, rows, V, H, lm_mode);
     } else if (tp_fused_ar) {
       uint32_t* flags0 = reinterpret_cast<uint32_t*>(ar_peer[0] + lg_off + lg_logits_bytes());  // in rank 0's memory
@@ -1378,12 +1765,11 @@ struct tgis_engine {
     const tgis_config& c = cfg;
     const int H = c.hidden, V = c.vocab;
     CK(cudaMemcpyAsync(d_stage.p, h_stage, copy_bytes, cudaMemcpyHostToDevice, stream));
-    if (need_norm && !opt) {  // no sampled row in the step -> its final norm has not run yet (OPT: always run)
+    if (need_norm && !opt && !pnx_on) {  // no sampled row in the step -> its final norm has not run yet (OPT: always run)
       CK(add_rmsnorm_launch(tmp.p, resid.p, final_norm, xn.p, T, H, c.rms_eps, stream));
       ++n_launches;
     }
-    CK(gather_rows_launch(xn.p, ds<int32_t>(off_samplesrc), last_hidden.p, m, H, stream));
-    ++n_launches;
+    gather_final_rows(m);
     lm_head_logits(m, lg_idx);
     if (rank == 0) {
       CK(sampler_launch(logits_ptr(), logits_bf16 ? 1 : 0, V, V, ds<SampleRow>(off_rows), m, seen_bitmap.p, bitmap_words,
@@ -1488,6 +1874,7 @@ struct tgis_engine {
     SampleRow* rows = hs<SampleRow>(off_rows);
     int32_t* bt = hs<int32_t>(off_bt);
     const int S = (int)batch.size();
+    step_n_ltiles = 0;
     for (int s = 0; s < S; ++s) {
       Request& r = *batch[s].r;
       const int q_len = batch[s].q_len;
@@ -1509,6 +1896,11 @@ struct tgis_engine {
           const int p = r.n_computed + j;
           if (p + 1 < r.n_prompt) prompt_rows.push_back(PromptRow{T + j, r.tokens[p + 1], p + 1, &r});
         }
+      }
+      if (pnx_on) {  // latent-attention query tiles: prompts, portions and single tokens alike
+        LatentTile* lt = hs<LatentTile>(off_ltiles);
+        for (int q0 = 0; q0 < q_len; q0 += pnx_tile_tokens)
+          lt[step_n_ltiles++] = LatentTile{s, q0, std::min(pnx_tile_tokens, q_len - q0), 0};
       }
       if (q_len == 1) {
         decids[n_dec++] = s;
@@ -1743,6 +2135,108 @@ struct tgis_engine {
     cv_out.notify_all();
   }
 
+  // ------------------------------------------------------------------------------------------------ trace replay
+  // lm_head over the listed rows of the step that has just run -> fp32 logits on the host, logit_rows_cap rows at a time
+  void logits_of_rows(const std::vector<int>& rows, int T, float* out) {
+    const int V = cfg.vocab;
+    bool need_norm = !opt && !pnx_on;  // the Llama stack leaves its last residual add + final norm to the sampling tail
+    for (size_t off = 0; off < rows.size(); off += (size_t)logit_rows_cap) {
+      const int m = (int)std::min<size_t>(logit_rows_cap, rows.size() - off);
+      int32_t* src = hs<int32_t>(off_samplesrc);
+      for (int i = 0; i < m; ++i) src[i] = rows[off + i];
+      CK(cudaMemcpyAsync(d_stage.p + off_samplesrc, h_stage + off_samplesrc, sizeof(int32_t) * m, cudaMemcpyHostToDevice,
+                         stream));
+      if (need_norm) {
+        CK(add_rmsnorm_launch(tmp.p, resid.p, final_norm, xn.p, T, cfg.hidden, cfg.rms_eps, stream));
+        ++n_launches;
+        need_norm = false;
+      }
+      gather_final_rows(m);
+      lm_head_logits(m, 1);
+      CK(cudaMemcpyAsync(h_trace_logits, logits.p, (size_t)m * V * lsz, cudaMemcpyDeviceToHost, stream));
+      CK(cudaStreamSynchronize(stream));
+      d2h_bytes += (long long)m * V * lsz;
+      float* dst = out + off * V;
+      if (logits_bf16) {
+        const bf16* hb = reinterpret_cast<const bf16*>(h_trace_logits);
+        for (size_t i = 0; i < (size_t)m * V; ++i) dst[i] = __bfloat162float(hb[i]);
+      } else {
+        memcpy(dst, h_trace_logits, (size_t)m * V * sizeof(float));
+      }
+    }
+  }
+
+  int trace_step(const tgis_trace_entry* entries, int n_entries, const char* const* end_ids, int n_end, float* logits_out) {
+    if (tp > 1) throw CudaError("trace replay runs on a single GPU");
+    if (n_entries > S_max) throw CudaError("more entries than sequence slots in one step");
+    std::vector<Request*> req(n_entries, nullptr);
+    int T = 0;
+    for (int i = 0; i < n_entries; ++i) {
+      const tgis_trace_entry& en = entries[i];
+      if (!en.request_id || !en.tokens || en.n_tokens < 1) throw CudaError("bad trace entry");
+      for (int j = 0; j < i; ++j)
+        if (strcmp(entries[j].request_id, en.request_id) == 0) throw CudaError("a request appears twice in one step");
+      for (auto& r : running)
+        if (r->id == en.request_id) req[i] = r.get();
+      if (!req[i]) {  // admitted at its first entry
+        if (free_slots.empty() || (int)running.size() >= S_max) throw CudaError("no free sequence slot for " + std::string(en.request_id));
+        auto r = std::make_unique<Request>();
+        r->id = en.request_id;
+        r->slot = free_slots.back();
+        free_slots.pop_back();
+        r->ts_arrival = now_s();
+        req[i] = r.get();
+        running.push_back(std::move(r));
+      }
+      Request& r = *req[i];
+      for (int j = 0; j < en.n_tokens; ++j) {
+        if (en.tokens[j] < 0 || en.tokens[j] >= cfg.vocab) throw CudaError("token id out of range");
+        r.tokens.push_back(en.tokens[j]);
+      }
+      r.n_prompt = (int)r.tokens.size();
+      if ((int)r.tokens.size() > cfg.max_model_len) throw CudaError("request longer than max_model_len");
+      if (!ensure_blocks(r, (int)r.tokens.size())) throw CudaError("cache pool exhausted");
+      for (int j = 0; j < en.n_want; ++j)
+        if (en.want[j] < 0 || en.want[j] >= en.n_tokens) throw CudaError("wanted position outside the entry");
+      T += en.n_tokens;
+    }
+    if (T > T_max) throw CudaError("step exceeds max_batched_tokens");
+    // the step order of step(): single tokens first, then the portions
+    std::vector<int> order;
+    for (int pass = 0; pass < 2; ++pass)
+      for (int i = 0; i < n_entries; ++i)
+        if ((entries[i].n_tokens == 1) == (pass == 0)) order.push_back(i);
+    std::vector<Sched> batch;
+    std::vector<int> row0(n_entries, 0);
+    int at = 0;
+    for (int i : order) {
+      batch.push_back(Sched{req[i], entries[i].n_tokens, false});
+      row0[i] = at;
+      at += entries[i].n_tokens;
+    }
+    if (!batch.empty()) {
+      run_batch(batch);
+      ++n_steps;
+      for (Sched& s : batch) s.r->n_computed += s.q_len;
+      std::vector<int> rows;
+      for (int i = 0; i < n_entries; ++i)
+        for (int j = 0; j < entries[i].n_want; ++j) rows.push_back(row0[i] + entries[i].want[j]);
+      if (!rows.empty()) {
+        if (!logits_out) throw CudaError("logits wanted but no output buffer");
+        logits_of_rows(rows, T, logits_out);
+      }
+    }
+    for (int k = 0; k < n_end; ++k)
+      for (size_t i = 0; i < running.size(); ++i)
+        if (running[i]->id == end_ids[k]) {
+          free_request(*running[i]);
+          running.erase(running.begin() + i);
+          break;
+        }
+    snapshot();
+    return 0;
+  }
+
   // one engine step; returns false when there was nothing to do
   bool step() {
     if (debug_step_sleep_us > 0) usleep(debug_step_sleep_us);  // experiment: GPU idle time between steps
@@ -1954,6 +2448,7 @@ int tgis_abi_version(void) { return TGIS_ABI_VERSION; }
 int tgis_engine_create(const tgis_config* cfg, tgis_engine** out) {
   if (!cfg || !out) return fail("null argument");
   if (cfg->abi_version != TGIS_ABI_VERSION) return fail("ABI version mismatch");
+  if (cfg->arch == TGIS_ARCH_PONENEX) return fail("this architecture is described layer by layer: use tgis_engine_create_spec");
   if (cfg->arch != TGIS_ARCH_LLAMA && cfg->arch != TGIS_ARCH_OPT) return fail("unknown arch");
   if (cfg->arch == TGIS_ARCH_OPT) {
     if (cfg->head_dim != 64 && cfg->head_dim != HEAD_DIM) return fail("OPT: head_dim must be 64 or 128");
@@ -1985,6 +2480,53 @@ int tgis_engine_create(const tgis_config* cfg, tgis_engine** out) {
     return fail("no CUDA device: the TGIS engine has no CPU fallback");
   auto* e = new tgis_engine();
   e->cfg = *cfg;
+  try {
+    e->init();
+  } catch (const std::exception& ex) {
+    std::string m = ex.what();
+    delete e;
+    return fail(m);
+  }
+  *out = e;
+  return 0;
+}
+
+int tgis_engine_create_spec(const tgis_config* cfg, const tgis_model_spec* spec, tgis_engine** out) {
+  if (!cfg || !spec || !out || !spec->layers) return fail("null argument");
+  if (cfg->abi_version != TGIS_ABI_VERSION) return fail("ABI version mismatch");
+  if (cfg->arch != TGIS_ARCH_PONENEX) return fail("tgis_engine_create_spec: arch must be TGIS_ARCH_PONENEX");
+  if (spec->n_layers < 1 || spec->n_layers > 4096) return fail("bad n_layers");
+  if (spec->dtype != TGIS_DTYPE_BF16 && spec->dtype != TGIS_DTYPE_F32) return fail("dtype must be bf16 or fp32");
+  if (cfg->hidden < 1 || cfg->hidden > 12288 || cfg->vocab < 1) return fail("bad hidden / vocab");
+  if (cfg->tp_size > 1) return fail("this architecture runs on a single GPU only (tp_size must be 1)");
+  if (cfg->max_loras > 0) return fail("LoRA adapter slots are not supported for this architecture");
+  if (cfg->max_batched_tokens < 1 || cfg->max_num_seqs < 1 || cfg->max_model_len < 2) return fail("bad limits");
+  for (int i = 0; i < spec->n_layers; ++i) {
+    const tgis_layer_spec& s = spec->layers[i];
+    const std::string at = " (layer " + std::to_string(i) + ")";
+    if (s.mixer != TGIS_MIXER_LATENT_ATTENTION) return fail("unknown mixer type" + at);
+    if (s.heads < 1 || s.dim < 1 || s.rot_dim < 0 || s.vdim < 1 || s.kv_rank < 1 || s.q_rank < 1) return fail("bad mixer sizes" + at);
+    if (s.kv_rank > 512) return fail("kv_rank > 512 unsupported" + at);
+    if (s.rot_dims < 0 || s.rot_dims > s.rot_dim || (s.rot_dims & 1)) return fail("rot.dims must be even and <= rot_dim" + at);
+    if (s.mlp != TGIS_MLP_NONE && s.mlp != TGIS_MLP_MOE) return fail("unknown feed-forward kind" + at);
+    if (s.mlp == TGIS_MLP_MOE && (s.experts < 1 || s.top < 1 || s.top > s.experts || s.top > 32 || s.expert_ff < 1 ||
+                                  s.shared_ff < 0 || s.experts > 2048))
+      return fail("bad mixture-of-experts sizes" + at);
+  }
+  int ndev = 0;
+  if (cudaGetDeviceCount(&ndev) != cudaSuccess || ndev == 0)
+    return fail("no CUDA device: the TGIS engine has no CPU fallback");
+  auto* e = new tgis_engine();
+  e->cfg = *cfg;
+  e->cfg.n_layers = spec->n_layers;
+  e->cfg.n_q_heads = e->cfg.n_kv_heads = 1;  // (unused by this architecture; kept sane for the shared set-up code)
+  e->cfg.head_dim = HEAD_DIM;
+  e->cfg.ffn = 64;
+  e->cfg.tp_size = 1;
+  e->cfg.tp_rank = 0;
+  e->pnx_spec = *spec;
+  e->pnx_layer_specs.assign(spec->layers, spec->layers + spec->n_layers);
+  e->pnx_spec.layers = nullptr;
   try {
     e->init();
   } catch (const std::exception& ex) {
@@ -2040,6 +2582,18 @@ int tgis_engine_run_until_idle(tgis_engine* e) {
     return fail(ex.what());
   }
   return steps;
+}
+
+int tgis_engine_trace_step(tgis_engine* e, const tgis_trace_entry* entries, int32_t n_entries, const char* const* end_ids,
+                           int32_t n_end, float* logits_out) {
+  if (!e || (n_entries > 0 && !entries) || (n_end > 0 && !end_ids) || n_entries < 0 || n_end < 0) return fail("bad argument");
+  if (engine_prepare_sync(e) != 0) return -1;
+  try {
+    return e->trace_step(entries, n_entries, end_ids, n_end, logits_out);
+  } catch (const std::exception& ex) {
+    e->fail_all(ex.what());
+    return fail(ex.what());
+  }
 }
 
 int tgis_engine_add_request(tgis_engine* e, const char* request_id, const int32_t* prompt_ids, int32_t n_prompt,

@@ -230,6 +230,102 @@ cudaError_t attn_prefill_launch(const __nv_bfloat16* qkv, int qkv_ld, const __nv
                                 const int32_t* tile_q0, int n_tiles, const int32_t* block_table, int bt_stride,
                                 __nv_bfloat16* out, int out_ld, int n_q, int n_kv, float scale, cudaStream_t stream);
 
+// ---- element types of the kernels that run more than one (gemm_any.cu, attention_latent.cu, moe.cu, the fp32-residual norms)
+constexpr int DT_F32 = 0, DT_BF16 = 1;
+inline size_t dt_size(int dt) { return dt == DT_BF16 ? 2 : 4; }
+
+// ---- gemm_any.cu: Y = X W^T for any shape, bf16 or fp32 operands, dense / batched / grouped (see the file's header) -----
+constexpr int GEMM_ANY_PLAIN = 0;     // Y[row, n] = acc
+constexpr int GEMM_ANY_SWIGLU = 1;    // W rows interleaved (gate_j, up_j): Y[row, j] = silu(acc[2j]) * acc[2j + 1], N = 2 ff
+constexpr int GEMM_ANY_ROWSCALE = 2;  // Y[row, n] = acc * row_scale[row * scale_ld + batch index]
+struct GemmAny {
+  const void* X; const void* W; void* Y;
+  int x_dtype, w_dtype, y_dtype;   // DT_*
+  int T, N, K;                     // rows of X (grouped: total rows over all segments), rows of W, reduction length
+  int ldx, ldw, ldy;               // leading dimensions in elements
+  int batch;                       // > 1: blockIdx.z problems, operands x_bs / w_bs / y_bs elements apart
+  long long x_bs, w_bs, y_bs;
+  const int* seg_off;              // grouped: [n_groups + 1] row offsets on the device (nullptr: dense)
+  int n_groups;
+  long long w_gs;                  // elements between the weight matrices of consecutive groups
+  const int* gather;               // grouped: X row of position p = gather[p] / gather_div (nullptr: p itself)
+  int gather_div;
+  int mode;                        // GEMM_ANY_*
+  const float* row_scale; int scale_ld;
+};
+cudaError_t gemm_any_launch(const GemmAny& a, cudaStream_t stream);
+
+// ---- norms over an fp32 residual stream (elementwise.cu) ------------------------------------------------------------
+// out[t] = x[t] / sqrt(mean(x[t]^2) + eps) * (w_off + w)      x fp32 [T, ldx], n columns normed; out: DT_* [T, ldo]
+cudaError_t rmsnorm_f32_launch(const float* x, int ldx, const float* w, float w_off, void* out, int out_dtype, int ldo, int T,
+                               int n, float eps, cudaStream_t stream);
+// resid[t] = table[tok[t]] * scale   (fp32 residual stream from a bf16 / fp32 embedding table)
+cudaError_t embed_scale_f32_launch(const int32_t* token_ids, const void* table, int table_dtype, float scale, float* resid,
+                                   int T, int hidden, int vocab, cudaStream_t stream);
+// One sublayer's tail on an fp32 residual stream, row per CTA:
+//   y[t]      = y_main[t]                                               (y_main != nullptr), or the mixture
+//             = sum_k mix_w[t, k] * y_rows[inv[t * top + k]] + side_gate[t] * y_side[t]     (terms with null pointers drop out)
+//   resid[t] += mult * rmsnorm(y[t]) * (w_off + w_post)
+//   out[t]    = rmsnorm(resid[t]) * (w_off + w_pre)                      (w_pre != nullptr: the next sublayer's input)
+struct ResidTail {
+  const float* y_main;
+  const float* y_rows; const int32_t* inv; const float* mix_w; int top;
+  const float* y_side; const float* side_gate;
+  const float* w_post; const float* w_pre;
+  float* resid; void* out; int out_dtype;
+  float mult, w_off, eps;
+};
+cudaError_t resid_tail_launch(const ResidTail& a, int T, int hidden, cudaStream_t stream);
+// rows of any DT_* matrix: out[r, :] = x[rows[r], :]
+cudaError_t gather_rows_any_launch(const void* x, const int32_t* rows, void* out, int R, int hidden, int dtype,
+                                   cudaStream_t stream);
+// dst[r * rs + c * cs] = src[r, c]   (bf16 checkpoint tensor -> DT_* arena slice; transposes and row interleaves at load time)
+cudaError_t weight_place_launch(const __nv_bfloat16* src, int rows, int cols, void* dst, int dst_dtype, long long rs,
+                                long long cs, cudaStream_t stream);
+
+// ---- attention_latent.cu: attention over a cached low-rank latent (one shared key/value row per token) ---------------
+// A token's cache row is [c (kv_rank) | k_rot (rot_dim)]; with the per-head up-projections folded into the query and
+// the output ("absorbed" form) every head scores and sums the SAME rows:
+//   score_h(i, j) = scale * (q_abs_h(i) . c(j) + q_rot_h(i) . k_rot(j)),  q_abs_h = W_uk,h^T q_nope_h
+//   o_h(i)        = W_uv,h sum_j p_h(i, j) c(j)
+// Visibility: causal, and with window > 0 only the last `window` positions (0 <= i - j < window).
+struct LatentGeom {
+  int heads, dim, rot_dim, vdim, kv_rank, q_rank, window;
+  int rot_dims;      // the first rot_dims of the rot_dim rotated dims turn ("rotate half": i pairs with i + rot_dims / 2)
+  float scale;
+  __host__ __device__ int row() const { return kv_rank + rot_dim; }   // cache row / absorbed query length
+};
+// y [T, ldy] fp32 = the fused down-projection [q latent (q_rank) | kv latent (kv_rank) | k_rot (rot_dim) | gate (heads)]:
+//   cq[t]    = rmsnorm(q latent) * w_q            -> DT_* [T, q_rank]
+//   cache[slot[t]] = [rmsnorm(kv latent) * w_kv | rotary(k_rot, pos[t])]   (slot < 0: not cached)
+//   gate[t]  = sigmoid(gate logits)               -> fp32 [T, heads]       (heads_gate == 0: no gate columns)
+// cos_sin: fp32 [max_pos][rot_dims] = cos (rot_dims / 2) | sin (rot_dims / 2)
+cudaError_t latent_prep_launch(const float* y, int ldy, const LatentGeom& g, const float* w_q, const float* w_kv, float eps,
+                               const int32_t* positions, const int32_t* slot_mapping, const float* cos_sin, void* cq,
+                               void* cache, int dtype, float* gate, int T, cudaStream_t stream);
+// q [T, heads * (dim + rot_dim)] fp32 -> q_abs[t, h, kv_rank ..] = rotary(q_rot_h, pos[t])   (the first kv_rank entries of
+// every head are written by the absorbing batched product)
+cudaError_t latent_q_rope_launch(const float* q, const LatentGeom& g, const int32_t* positions, const float* cos_sin,
+                                 float* q_abs, int T, cudaStream_t stream);
+struct LatentTile {  // one CTA's queries: tokens [q0, q0 + nq) of the step's sequence `seq` (device array)
+  int32_t seq, q0, nq, pad;
+};
+constexpr int LATENT_PAIRS = 16;  // (token, head) pairs per CTA
+inline int latent_tile_tokens(int heads) { return heads >= LATENT_PAIRS ? 1 : LATENT_PAIRS / heads; }
+// q_abs fp32 [T, heads, row()], cache DT_* [num_blocks][KV_BLOCK][row()], o_lat fp32 [T, heads, kv_rank]
+cudaError_t latent_attn_launch(const float* q_abs, const void* cache, int dtype, const AttnSeq* seqs,
+                               const LatentTile* tiles, int n_tiles, const int32_t* block_table, int bt_stride,
+                               float* o_lat, const LatentGeom& g, cudaStream_t stream);
+
+// ---- moe.cu: top-k router and the bookkeeping of the grouped expert products ----------------------------------------
+// logits fp32 [T, ld] (columns [0, E): experts; column E, when side_gate != nullptr: the shared expert's gate logit):
+//   ids[t, k], w[t, k] = the `top` largest of logits + bias and the softmax over just those;  side_gate[t] = sigmoid(.)
+cudaError_t moe_route_launch(const float* logits, int ld, const float* bias, int E, int top, int32_t* ids, float* w,
+                             float* side_gate, int T, cudaStream_t stream);
+// seg_off[E + 1]: rows per expert, prefix-summed; order[p] = t * top + k of the p-th row; inv[t * top + k] = p
+cudaError_t moe_align_launch(const int32_t* ids, int T, int top, int E, int32_t* seg_off, int32_t* order, int32_t* inv,
+                             cudaStream_t stream);
+
 // ---- sampler.cu --------------------------------------------------------------------------------------------------
 constexpr int MAX_TOPN = 12;  // reference forces max_logprobs >= 11 (tgis_utils/args.py:214-216)
 struct SampleRow {            // per sampled row parameters (device array, 64 B)

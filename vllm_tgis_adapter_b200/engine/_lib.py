@@ -10,8 +10,11 @@ import ctypes as C
 import os
 from pathlib import Path
 
-ABI_VERSION = 7
-ARCH_LLAMA, ARCH_OPT = 0, 1
+ABI_VERSION = 8
+ARCH_LLAMA, ARCH_OPT, ARCH_PONENEX = 0, 1, 2
+MIXER_LATENT_ATTENTION = 1
+MLP_NONE, MLP_MOE = 0, 1
+DTYPE_BF16, DTYPE_F32 = 0, 1
 MAX_REQUEST_ID = 96
 MAX_TOPN = 12
 MAX_STOP_TOKEN_IDS = 8
@@ -29,6 +32,29 @@ class TgisConfig(C.Structure):
         ("use_cuda_graphs", C.c_int32), ("debug_gemm_ref", C.c_int32), ("seed", C.c_uint64),
         ("nccl_id", C.c_uint8 * 128), ("shm_name", C.c_char * 64),
         ("max_loras", C.c_int32), ("max_lora_rank", C.c_int32), ("arch", C.c_int32), ("reserved0", C.c_int32),
+    ]
+
+
+class TgisLayerSpec(C.Structure):
+    _fields_ = [
+        ("mixer", C.c_int32), ("heads", C.c_int32), ("dim", C.c_int32), ("rot_dim", C.c_int32), ("vdim", C.c_int32),
+        ("kv_rank", C.c_int32), ("q_rank", C.c_int32), ("window", C.c_int32), ("rot_dims", C.c_int32),
+        ("rot_base", C.c_float), ("scale", C.c_float), ("mlp", C.c_int32), ("experts", C.c_int32), ("top", C.c_int32),
+        ("expert_ff", C.c_int32), ("shared_ff", C.c_int32), ("reserved", C.c_int32),
+    ]
+
+
+class TgisModelSpec(C.Structure):
+    _fields_ = [
+        ("n_layers", C.c_int32), ("dtype", C.c_int32), ("embed_scale", C.c_float), ("residual_mult", C.c_float),
+        ("norm_eps", C.c_float), ("reserved", C.c_int32), ("layers", C.POINTER(TgisLayerSpec)),
+    ]
+
+
+class TgisTraceEntry(C.Structure):
+    _fields_ = [
+        ("request_id", C.c_char_p), ("tokens", C.POINTER(C.c_int32)), ("n_tokens", C.c_int32), ("n_want", C.c_int32),
+        ("want", C.POINTER(C.c_int32)),
     ]
 
 
@@ -69,7 +95,7 @@ class TgisStatus(C.Structure):
 
 # Every symbol include/tgis_engine.h and include/tgis_kernels.h declare (tests/test_abi_cpu.py checks the export list)
 ENGINE_SYMBOLS = [
-    "tgis_last_error", "tgis_abi_version", "tgis_engine_create", "tgis_engine_load_weight", "tgis_engine_start",
+    "tgis_last_error", "tgis_abi_version", "tgis_engine_create", "tgis_engine_create_spec", "tgis_engine_trace_step", "tgis_engine_load_weight", "tgis_engine_start",
     "tgis_engine_add_request", "tgis_engine_abort", "tgis_engine_set_mask_provider", "tgis_engine_load_adapter_weight", "tgis_engine_clear_adapter", "tgis_engine_poll", "tgis_engine_status",
     "tgis_engine_max_model_len", "tgis_engine_set_profiling", "tgis_nccl_unique_id", "tgis_engine_worker_run", "tgis_engine_shutdown", "tgis_engine_destroy", "tgis_engine_run_until_idle",
 ]
@@ -109,6 +135,8 @@ def load_library() -> C.CDLL:
     lib.tgis_last_error.restype = C.c_char_p
     lib.tgis_k_last_error.restype = C.c_char_p
     lib.tgis_engine_create.argtypes = [C.POINTER(TgisConfig), C.POINTER(vp)]
+    lib.tgis_engine_create_spec.argtypes = [C.POINTER(TgisConfig), C.POINTER(TgisModelSpec), C.POINTER(vp)]
+    lib.tgis_engine_trace_step.argtypes = [vp, C.POINTER(TgisTraceEntry), i32, C.POINTER(C.c_char_p), i32, C.POINTER(f32)]
     lib.tgis_engine_load_weight.argtypes = [vp, C.c_char_p, vp, i64, i64, i32]
     lib.tgis_engine_start.argtypes = [vp]
     lib.tgis_engine_add_request.argtypes = [vp, C.c_char_p, C.POINTER(i32), i32, C.POINTER(TgisSamplingParams)]

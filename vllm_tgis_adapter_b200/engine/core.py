@@ -30,6 +30,11 @@ class ModelConfig:
     rms_eps: float = 1e-5
     max_model_len: int = 2048
     arch: str = "llama"
+    # arch "ponenex" (engine/ponenex.py): the layers are described one by one; n_q_heads / n_kv_heads / ffn are unused
+    layers: list | None = None          # list[ponenex.LayerSpec]
+    embed_scale: float = 1.0
+    residual_mult: float = 1.0
+    dtype: str = "bfloat16"             # "bfloat16" | "float32" (ponenex only)
 
 
 # Named architectures (real dims; this offline build runs them on synthetic weights — SURVEY.md §0)
@@ -47,6 +52,17 @@ PRESETS: dict[str, ModelConfig] = {
     "llama3-70b": ModelConfig(n_layers=80, hidden=8192, n_q_heads=64, n_kv_heads=8, ffn=28672, vocab=128256,
                               max_model_len=8192),
 }
+
+
+KV_BLOCK_TOKENS = 32   # tokens per cache block (csrc/kernels.h KV_BLOCK)
+
+
+def cache_block_bytes(mc: ModelConfig) -> int:
+    """Bytes one cache block takes over all layers (what `kv_cache_bytes` is divided by)."""
+    if mc.arch == "ponenex":
+        esz = 4 if mc.dtype == "float32" else 2
+        return KV_BLOCK_TOKENS * esz * sum(l.kv_rank + l.rot_dim for l in mc.layers)
+    return 2 * mc.n_layers * mc.n_kv_heads * KV_BLOCK_TOKENS * 128 * 2
 
 
 @dataclasses.dataclass
@@ -131,12 +147,18 @@ class NativeEngine:
             cfg.shm_name = shm_name.encode()
         cfg.use_cuda_graphs, cfg.debug_gemm_ref, cfg.seed = int(use_cuda_graphs), 1 if debug_gemm_ref else 0, seed
         cfg.max_loras, cfg.max_lora_rank = int(max_loras), int(max_lora_rank) if max_loras else 0
-        if model.arch not in ("llama", "opt"):
+        if model.arch not in ("llama", "opt", "ponenex"):
             raise EngineError(f"unknown architecture {model.arch!r}")
-        cfg.arch = _lib.ARCH_OPT if model.arch == "opt" else _lib.ARCH_LLAMA
+        cfg.arch = {"llama": _lib.ARCH_LLAMA, "opt": _lib.ARCH_OPT, "ponenex": _lib.ARCH_PONENEX}[model.arch]
         self.max_loras, self.max_lora_rank = int(max_loras), int(max_lora_rank)
         self._h = C.c_void_p()
-        if self.lib.tgis_engine_create(C.byref(cfg), C.byref(self._h)) != 0:
+        if model.arch == "ponenex":
+            from .ponenex import model_spec
+
+            spec, _keep = model_spec(model)   # _keep: the ctypes layer array the spec points into
+            if self.lib.tgis_engine_create_spec(C.byref(cfg), C.byref(spec), C.byref(self._h)) != 0:
+                raise EngineError(f"tgis_engine_create_spec failed: {_lib.last_error(self.lib)}")
+        elif self.lib.tgis_engine_create(C.byref(cfg), C.byref(self._h)) != 0:
             raise EngineError(f"tgis_engine_create failed: {_lib.last_error(self.lib)}")
         self._poll_buf = (TgisStepOutput * 512)()
 
@@ -208,6 +230,31 @@ class NativeEngine:
                 n_output_tokens=o.n_output_tokens, ts_arrival=o.ts_arrival, ts_first_scheduled=o.ts_first_scheduled,
                 ts_first_token=o.ts_first_token, ts_last_token=o.ts_last_token, prompt_pos=o.prompt_pos, token_id=o.token_id))
         return outs
+
+    def trace_step(self, entries: list[tuple[str, list[int], list[int]]], end: Iterable[str] = ()):
+        """One replay step: entries = [(request id, its next tokens, wanted positions among them)]; `end`: requests that
+        are finished after the step.  Returns fp32 logits [sum of wanted, vocab] (numpy) in entry / want order."""
+        import numpy as np
+
+        n = len(entries)
+        arr = (_lib.TgisTraceEntry * max(n, 1))()
+        keep = []
+        n_want = 0
+        for i, (rid, toks, want) in enumerate(entries):
+            t = (C.c_int32 * len(toks))(*toks)
+            w = (C.c_int32 * max(len(want), 1))(*want)
+            keep += [t, w]
+            arr[i].request_id = rid.encode()
+            arr[i].tokens, arr[i].n_tokens = t, len(toks)
+            arr[i].want, arr[i].n_want = w, len(want)
+            n_want += len(want)
+        ends = [e.encode() for e in end]
+        end_arr = (C.c_char_p * max(len(ends), 1))(*ends)
+        out = np.empty((n_want, self.model.vocab), dtype=np.float32)
+        optr = out.ctypes.data_as(C.POINTER(C.c_float)) if n_want else None
+        if self.lib.tgis_engine_trace_step(self._h, arr, n, end_arr, len(ends), optr) != 0:
+            raise EngineError(f"trace_step failed: {_lib.last_error(self.lib)}")
+        return out
 
     def run_until_idle(self) -> int:
         n = self.lib.tgis_engine_run_until_idle(self._h)

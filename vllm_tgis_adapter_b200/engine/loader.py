@@ -18,8 +18,12 @@ from .tokenizer import load_tokenizer
 logger = logging.getLogger("vllm_tgis_adapter.engine")
 
 
-def model_config_from_hf(path: Path, max_model_len: int | None) -> ModelConfig:
+def model_config_from_hf(path: Path, max_model_len: int | None, dtype: str = "bfloat16") -> ModelConfig:
     cfg = json.loads((path / "config.json").read_text())
+    if cfg.get("architecture") == "Ponenex":
+        from .ponenex import model_config_from_json
+
+        return model_config_from_json(cfg, max_model_len, dtype)
     archs = cfg.get("architectures") or []
     if cfg.get("model_type") == "opt" or any("OPT" in a for a in archs):
         return _opt_model_config(cfg, max_model_len)
@@ -86,6 +90,12 @@ def load_synthetic_weights(eng: NativeEngine, mc: ModelConfig, seed: int, device
 
     def rnd(r, c):
         return (torch.randn(r, c, generator=gen, device=f"cuda:{device}", dtype=torch.float32) * 0.02).to(torch.bfloat16)
+
+    if mc.arch == "ponenex":
+        from .ponenex import synthetic_weights
+
+        eng.load_weights(synthetic_weights(mc, seed, f"cuda:{device}"))
+        return
 
     if mc.arch == "opt":
         # HF OPT parameter names; LayerNorm weights around 1, small random biases (HF's init has zeros: random ones exercise
@@ -159,7 +169,11 @@ def _resolve_model(args):
         raise ValueError("--model / --model-name is required")
     path = Path(args.model)
     if path.is_dir():
-        return model_config_from_hf(path, args.max_model_len), path
+        dtype = "float32" if getattr(args, "dtype", "auto") in ("float32", "fp32") else "bfloat16"
+        mc = model_config_from_hf(path, args.max_model_len, dtype)
+        if dtype == "float32" and mc.arch != "ponenex":
+            raise ValueError(f"--dtype float32 is not available for the {mc.arch} architecture (bfloat16 only)")
+        return mc, path
     if args.model in PRESETS:
         if not args.synthetic_weights:
             raise ValueError(f"--model {args.model} is a preset name: pass --synthetic-weights or a model directory")
@@ -179,7 +193,7 @@ def _make_native_engine(args, mc: ModelConfig, path, device: int, **tp_kw) -> Na
         load_safetensors_dir(eng, path)      # full tensors: a tensor-parallel engine keeps its rank's shard
     else:
         load_synthetic_weights(eng, mc, args.seed, device)
-    if mc.arch != "opt":   # OPT has learned positions (part of the checkpoint), no rotary table
+    if mc.arch not in ("opt", "ponenex"):   # OPT: learned positions; Ponenex: per-layer tables built by the engine
         eng.load_weight("tgis.rope_cos_sin", rope_cos_sin(mc))
     return eng
 

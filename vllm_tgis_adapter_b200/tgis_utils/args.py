@@ -79,7 +79,7 @@ def make_engine_arg_parser() -> argparse.ArgumentParser:
     p.add_argument("--model", type=str, default=None, help="model directory (HF layout) or a preset name")
     p.add_argument("--tokenizer", type=str, default=None)
     p.add_argument("--max-model-len", type=int, default=None)
-    p.add_argument("--dtype", type=str, default="auto", choices=["auto", "bfloat16", "bf16"])
+    p.add_argument("--dtype", type=str, default="auto", choices=["auto", "bfloat16", "bf16", "float32", "fp32"])
     p.add_argument("--tensor-parallel-size", "-tp", type=int, default=None)
     p.add_argument("--max-num-seqs", type=int, default=256)
     p.add_argument("--max-num-batched-tokens", type=int, default=8192)
