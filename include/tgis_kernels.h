@@ -108,6 +108,42 @@ int tgis_k_sizeof_sample_row(void);
 int tgis_k_sizeof_sample_out(void);
 int tgis_k_kv_block(void);
 
+/* ---- kernels of the layer-list architectures (fp32 residual stream, latent attention, mixture of experts) ----------
+ * dtype codes: 0 = fp32, 1 = bf16.  All pointers are device memory unless marked host. */
+/* y = x w^T, any shape; batch > 1: one problem per batch index, operands *_bs elements apart; seg_off_dev != NULL: grouped
+ * (row segment g multiplies with weight matrix g, w_gs elements apart; x row of position p = gather[p] / gather_div);
+ * mode 0 plain, 1 SwiGLU over interleaved (gate, up) rows, 2 y *= row_scale[row * scale_ld + batch index] */
+int tgis_k_gemm_any(const void* x, const void* w, void* y, int32_t x_dt, int32_t w_dt, int32_t y_dt, int32_t T, int32_t N,
+                    int32_t K, int32_t ldx, int32_t ldw, int32_t ldy, int32_t batch, int64_t x_bs, int64_t w_bs, int64_t y_bs,
+                    const int32_t* seg_off_dev, int32_t n_groups, int64_t w_gs, const int32_t* gather_dev, int32_t gather_div,
+                    int32_t mode, const float* row_scale, int32_t scale_ld);
+int tgis_k_rmsnorm_f32(const float* x, int32_t ldx, const float* w, float w_off, void* out, int32_t out_dt, int32_t ldo,
+                       int32_t T, int32_t n, float eps);
+/* resid += mult * rmsnorm(y) * (w_off + w_post); out = rmsnorm(resid) * (w_off + w_pre) (w_pre may be NULL); y = y_main, or
+ * sum_k mix_w[t, k] * y_rows[inv[t * top + k]] + side_gate[t] * y_side[t] (NULL terms drop out) */
+int tgis_k_resid_tail(const float* y_main, const float* y_rows, const int32_t* inv, const float* mix_w, int32_t top,
+                      const float* y_side, const float* side_gate, const float* w_post, const float* w_pre, float* resid,
+                      void* out, int32_t out_dt, float mult, float w_off, float eps, int32_t T, int32_t hidden);
+typedef struct tgis_k_latent_geom {
+  int32_t heads, dim, rot_dim, vdim, kv_rank, q_rank, window, rot_dims;
+  float scale;
+} tgis_k_latent_geom;
+/* y [T, q_rank + kv_rank + rot_dim + heads] fp32 -> normed query latent (cq), cache row [normed kv latent | rotary key]
+ * at slot[t], sigmoid gates; cos_sin fp32 [positions][rot_dims] = cos | sin */
+int tgis_k_latent_prep(const float* y, int32_t ldy, const tgis_k_latent_geom* g, const float* w_q, const float* w_kv, float eps,
+                       const int32_t* positions, const int32_t* slots, const float* cos_sin, void* cq, void* cache,
+                       int32_t dt, float* gate, int32_t T);
+int tgis_k_latent_q_rope(const float* q, const tgis_k_latent_geom* g, const int32_t* positions, const float* cos_sin,
+                         float* q_abs, int32_t T);
+/* seqs_host: n_seqs x {q_start, q_len, kv_len, block_row}; block_table_host [rows][bt_stride]; q_abs fp32 [T, heads,
+ * kv_rank + rot_dim]; cache [blocks][32][kv_rank + rot_dim]; o_lat fp32 [T, heads, kv_rank] */
+int tgis_k_latent_attn(const float* q_abs, const void* cache, int32_t dt, const int32_t* seqs_host, int32_t n_seqs,
+                       const int32_t* block_table_host, int32_t bt_rows, int32_t bt_stride, float* o_lat,
+                       const tgis_k_latent_geom* g);
+int tgis_k_moe_route(const float* logits, int32_t ld, const float* bias, int32_t E, int32_t top, int32_t* ids, float* w,
+                     float* side_gate, int32_t T);
+int tgis_k_moe_align(const int32_t* ids, int32_t T, int32_t top, int32_t E, int32_t* seg_off, int32_t* order, int32_t* inv);
+
 #ifdef __cplusplus
 }
 #endif

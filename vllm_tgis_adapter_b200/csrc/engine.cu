@@ -264,6 +264,8 @@ struct tgis_engine {
   int pnx_tile_tokens = 1, step_n_ltiles = 0;
   size_t off_ltiles = 0;
   int logit_rows_cap = 0;                            // rows of the logits buffer (>= max_num_seqs)
+  int logits_ld = 0;                                 // its row length: the vocabulary rounded up to the sampler's 8-column
+                                                     // vectors; the padding columns hold -inf for good
   std::string pnx_dump_path;                         // TGIS_DUMP_RESID: append the residual stream after every layer (debug)
   // kv cache
   DevBuf<bf16> k_cache, v_cache;
@@ -497,6 +499,7 @@ struct tgis_engine {
     if (pnx_on) logits_bf16 = false;
     lsz = logits_bf16 ? 2 : 4;
     logit_rows_cap = std::max(S_max, 64);
+    logits_ld = pnx_on ? (c.vocab + 7) / 8 * 8 : c.vocab;
 
     const size_t H = c.hidden, F = Fl, V = c.vocab, L = c.n_layers;  // F: this rank's ffn shard
     if (!pnx_on) {
@@ -578,7 +581,13 @@ struct tgis_engine {
     }
     }  // !pnx_on
     last_hidden.alloc(S_alloc * H);
-    logits.alloc((size_t)logit_rows_cap * V * lsz);
+    logits.alloc((size_t)logit_rows_cap * logits_ld * lsz);
+    if (logits_ld != c.vocab) {  // (fp32 logits) columns [vocab, logits_ld): never written again, never chosen
+      std::vector<float> fill((size_t)logit_rows_cap * logits_ld, 0.f);
+      for (int r = 0; r < logit_rows_cap; ++r)
+        for (int j = c.vocab; j < logits_ld; ++j) fill[(size_t)r * logits_ld + j] = -INFINITY;
+      CK(cudaMemcpy(logits.p, fill.data(), fill.size() * sizeof(float), cudaMemcpyHostToDevice));
+    }
     if (tp > 1) {
       logits_shard.alloc((size_t)S_max * Vl * lsz);
       logits_gather.alloc((size_t)tp * S_max * Vl * lsz);
@@ -594,7 +603,7 @@ struct tgis_engine {
     const int G = c.n_q_heads / std::max(c.n_kv_heads, 1);
     part_o.alloc((size_t)S_max * nkv * max_splits_cap * G * HEAD_DIM);
     part_ml.alloc((size_t)S_max * nkv * max_splits_cap * G * 2);
-    samp_scratch.alloc((size_t)logit_rows_cap * V);
+    samp_scratch.alloc((size_t)logit_rows_cap * logits_ld);
     seen_bitmap.alloc((size_t)S_max * bitmap_words);
     seen_bitmap.zero();
     if (rank == 0) {  // only the sampling rank needs the masks
@@ -604,7 +613,7 @@ struct tgis_engine {
     d_samp_out.alloc(S_max);
     CK(cudaHostAlloc(&h_samp_out, sizeof(SampleOut) * S_max, cudaHostAllocDefault));
     CK(cudaHostAlloc(&h_plp_out, sizeof(SampleOut) * S_max, cudaHostAllocDefault));
-    CK(cudaHostAlloc(&h_trace_logits, (size_t)logit_rows_cap * V * sizeof(float), cudaHostAllocDefault));
+    CK(cudaHostAlloc(&h_trace_logits, (size_t)logit_rows_cap * logits_ld * sizeof(float), cudaHostAllocDefault));
 
     // ---- staging layout
     size_t o = 0;
@@ -1653,7 +1662,7 @@ struct tgis_engine {
       gather_final_rows(R);
       lm_head_logits(R, 1);
       if (rank == 0) {
-        CK(sampler_launch(logits_ptr(), logits_bf16 ? 1 : 0, V, V, ds<SampleRow>(off_rows), R, seen_bitmap.p, bitmap_words,
+        CK(sampler_launch(logits_ptr(), logits_bf16 ? 1 : 0, logits_ld, logits_ld, ds<SampleRow>(off_rows), R, seen_bitmap.p, bitmap_words,
                           samp_scratch.p, d_samp_out.p, stream, samp_complex & 1, num_sms,
                           (samp_complex & 2) ? allow_bitmap.p : nullptr));
         ++n_launches;
@@ -1734,7 +1743,7 @@ struct tgis_engine {
     const int H = c.hidden, V = c.vocab;
     const int lm_mode = logits_bf16 ? 0 : 1;
     if (pnx_on) {
-      pnx_gemm(pnx_last, pnx_dt, H, pnx_head, logits.p, DT_F32, V, rows, V, H);
+      pnx_gemm(pnx_last, pnx_dt, H, pnx_head, logits.p, DT_F32, logits_ld, rows, V, H);
     } else if (tp == 1) {
       gemm(xm_last, m_lm, last_hidden.p, lm_head, logits.p, rows, V, H, lm_mode);
     } else if (tp_fused_ar) {
@@ -1772,7 +1781,7 @@ struct tgis_engine {
     gather_final_rows(m);
     lm_head_logits(m, lg_idx);
     if (rank == 0) {
-      CK(sampler_launch(logits_ptr(), logits_bf16 ? 1 : 0, V, V, ds<SampleRow>(off_rows), m, seen_bitmap.p, bitmap_words,
+      CK(sampler_launch(logits_ptr(), logits_bf16 ? 1 : 0, logits_ld, logits_ld, ds<SampleRow>(off_rows), m, seen_bitmap.p, bitmap_words,
                         samp_scratch.p, d_samp_out.p, stream, /*any_complex=*/0, num_sms));
       ++n_launches;
       CK(cudaMemcpyAsync(h_plp_out, d_samp_out.p, sizeof(SampleOut) * m, cudaMemcpyDeviceToHost, stream));
@@ -2153,15 +2162,16 @@ struct tgis_engine {
       }
       gather_final_rows(m);
       lm_head_logits(m, 1);
-      CK(cudaMemcpyAsync(h_trace_logits, logits.p, (size_t)m * V * lsz, cudaMemcpyDeviceToHost, stream));
+      CK(cudaMemcpyAsync(h_trace_logits, logits.p, (size_t)m * logits_ld * lsz, cudaMemcpyDeviceToHost, stream));
       CK(cudaStreamSynchronize(stream));
-      d2h_bytes += (long long)m * V * lsz;
+      d2h_bytes += (long long)m * logits_ld * lsz;
       float* dst = out + off * V;
       if (logits_bf16) {
         const bf16* hb = reinterpret_cast<const bf16*>(h_trace_logits);
-        for (size_t i = 0; i < (size_t)m * V; ++i) dst[i] = __bfloat162float(hb[i]);
+        for (size_t i = 0; i < (size_t)m * V; ++i) dst[i] = __bfloat162float(hb[i]);  // (logits_ld == V)
       } else {
-        memcpy(dst, h_trace_logits, (size_t)m * V * sizeof(float));
+        for (int r = 0; r < m; ++r)
+          memcpy(dst + (size_t)r * V, h_trace_logits + (size_t)r * logits_ld, (size_t)V * sizeof(float));
       }
     }
   }

@@ -1,5 +1,6 @@
 // C-ABI test hooks (include/tgis_kernels.h): every hot-path kernel callable on raw device pointers so that the GPU
 // parity tests exercise exactly the code the engine runs, through the same shared library.
+#include <algorithm>
 #include <cstring>
 #include <string>
 #include <vector>
@@ -507,6 +508,96 @@ int tgis_k_silu_mul_interleaved(const void* gate_up_dev, void* act_dev, int32_t 
 int tgis_k_sampler(const void* logits_dev, int32_t ld, int32_t vocab, const void* rows_host, int32_t n_rows,
                    void* seen_bitmap_dev, void* out_host) {
   return tgis_k_sampler_ex(logits_dev, 0, ld, vocab, rows_host, n_rows, seen_bitmap_dev, out_host, 1, nullptr);
+}
+
+// ---- layer-list architectures ----------------------------------------------------------------------------------------
+int tgis_k_gemm_any(const void* x, const void* w, void* y, int32_t x_dt, int32_t w_dt, int32_t y_dt, int32_t T, int32_t N,
+                    int32_t K, int32_t ldx, int32_t ldw, int32_t ldy, int32_t batch, int64_t x_bs, int64_t w_bs, int64_t y_bs,
+                    const int32_t* seg_off_dev, int32_t n_groups, int64_t w_gs, const int32_t* gather_dev, int32_t gather_div,
+                    int32_t mode, const float* row_scale, int32_t scale_ld) {
+  GemmAny a{};
+  a.X = x; a.W = w; a.Y = y;
+  a.x_dtype = x_dt; a.w_dtype = w_dt; a.y_dtype = y_dt;
+  a.T = T; a.N = N; a.K = K; a.ldx = ldx; a.ldw = ldw; a.ldy = ldy;
+  a.batch = batch; a.x_bs = x_bs; a.w_bs = w_bs; a.y_bs = y_bs;
+  a.seg_off = seg_off_dev; a.n_groups = n_groups; a.w_gs = w_gs; a.gather = gather_dev; a.gather_div = gather_div;
+  a.mode = mode; a.row_scale = row_scale; a.scale_ld = scale_ld;
+  KCK(gemm_any_launch(a, 0));
+  KCK(cudaDeviceSynchronize());
+  return 0;
+}
+
+int tgis_k_rmsnorm_f32(const float* x, int32_t ldx, const float* w, float w_off, void* out, int32_t out_dt, int32_t ldo,
+                       int32_t T, int32_t n, float eps) {
+  KCK(rmsnorm_f32_launch(x, ldx, w, w_off, out, out_dt, ldo, T, n, eps, 0));
+  KCK(cudaDeviceSynchronize());
+  return 0;
+}
+
+int tgis_k_resid_tail(const float* y_main, const float* y_rows, const int32_t* inv, const float* mix_w, int32_t top,
+                      const float* y_side, const float* side_gate, const float* w_post, const float* w_pre, float* resid,
+                      void* out, int32_t out_dt, float mult, float w_off, float eps, int32_t T, int32_t hidden) {
+  ResidTail a{};
+  a.y_main = y_main; a.y_rows = y_rows; a.inv = inv; a.mix_w = mix_w; a.top = top; a.y_side = y_side; a.side_gate = side_gate;
+  a.w_post = w_post; a.w_pre = w_pre; a.resid = resid; a.out = out; a.out_dtype = out_dt;
+  a.mult = mult; a.w_off = w_off; a.eps = eps;
+  KCK(resid_tail_launch(a, T, hidden, 0));
+  KCK(cudaDeviceSynchronize());
+  return 0;
+}
+
+static LatentGeom to_geom(const tgis_k_latent_geom* g) {
+  return LatentGeom{g->heads, g->dim, g->rot_dim, g->vdim, g->kv_rank, g->q_rank, g->window, g->rot_dims, g->scale};
+}
+
+int tgis_k_latent_prep(const float* y, int32_t ldy, const tgis_k_latent_geom* g, const float* w_q, const float* w_kv, float eps,
+                       const int32_t* positions, const int32_t* slots, const float* cos_sin, void* cq, void* cache,
+                       int32_t dt, float* gate, int32_t T) {
+  KCK(latent_prep_launch(y, ldy, to_geom(g), w_q, w_kv, eps, positions, slots, cos_sin, cq, cache, dt, gate, T, 0));
+  KCK(cudaDeviceSynchronize());
+  return 0;
+}
+
+int tgis_k_latent_q_rope(const float* q, const tgis_k_latent_geom* g, const int32_t* positions, const float* cos_sin,
+                         float* q_abs, int32_t T) {
+  KCK(latent_q_rope_launch(q, to_geom(g), positions, cos_sin, q_abs, T, 0));
+  KCK(cudaDeviceSynchronize());
+  return 0;
+}
+
+int tgis_k_latent_attn(const float* q_abs, const void* cache, int32_t dt, const int32_t* seqs_host, int32_t n_seqs,
+                       const int32_t* block_table_host, int32_t bt_rows, int32_t bt_stride, float* o_lat,
+                       const tgis_k_latent_geom* g) {
+  const LatentGeom geom = to_geom(g);
+  std::vector<AttnSeq> seqs(n_seqs);
+  std::vector<LatentTile> tiles;
+  const int qt = latent_tile_tokens(geom.heads);
+  for (int i = 0; i < n_seqs; ++i) {
+    seqs[i] = AttnSeq{seqs_host[4 * i], seqs_host[4 * i + 1], seqs_host[4 * i + 2], seqs_host[4 * i + 3]};
+    for (int q0 = 0; q0 < seqs[i].q_len; q0 += qt) tiles.push_back(LatentTile{i, q0, std::min(qt, seqs[i].q_len - q0), 0});
+  }
+  Tmp<AttnSeq> d_seqs;
+  Tmp<LatentTile> d_tiles;
+  Tmp<int32_t> d_bt;
+  KCK(d_seqs.upload(seqs.data(), seqs.size()));
+  KCK(d_tiles.upload(tiles.data(), tiles.size()));
+  KCK(d_bt.upload(block_table_host, (size_t)bt_rows * bt_stride));
+  KCK(latent_attn_launch(q_abs, cache, dt, d_seqs.p, d_tiles.p, (int)tiles.size(), d_bt.p, bt_stride, o_lat, geom, 0));
+  KCK(cudaDeviceSynchronize());
+  return 0;
+}
+
+int tgis_k_moe_route(const float* logits, int32_t ld, const float* bias, int32_t E, int32_t top, int32_t* ids, float* w,
+                     float* side_gate, int32_t T) {
+  KCK(moe_route_launch(logits, ld, bias, E, top, ids, w, side_gate, T, 0));
+  KCK(cudaDeviceSynchronize());
+  return 0;
+}
+
+int tgis_k_moe_align(const int32_t* ids, int32_t T, int32_t top, int32_t E, int32_t* seg_off, int32_t* order, int32_t* inv) {
+  KCK(moe_align_launch(ids, T, top, E, seg_off, order, inv, 0));
+  KCK(cudaDeviceSynchronize());
+  return 0;
 }
 
 }  // extern "C"
