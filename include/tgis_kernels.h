@@ -133,12 +133,12 @@ typedef struct tgis_k_latent_geom {
 int tgis_k_latent_prep(const float* y, int32_t ldy, const tgis_k_latent_geom* g, const float* w_q, const float* w_kv, float eps,
                        const int32_t* positions, const int32_t* slots, const float* cos_sin, void* cq, void* cache,
                        int32_t dt, float* gate, int32_t T);
-int tgis_k_latent_q_rope(const float* q, const tgis_k_latent_geom* g, const int32_t* positions, const float* cos_sin,
-                         float* q_abs, int32_t T);
+int tgis_k_latent_q_rope(const void* q, int32_t q_dt, const tgis_k_latent_geom* g, const int32_t* positions,
+                         const float* cos_sin, float* q_abs, int32_t T);
 /* seqs_host: n_seqs x {q_start, q_len, kv_len, block_row}; block_table_host [rows][bt_stride]; q_abs fp32 [T, heads,
- * kv_rank + rot_dim]; cache [blocks][32][kv_rank + rot_dim]; o_lat fp32 [T, heads, kv_rank] */
+ * kv_rank + rot_dim]; cache [blocks][32][kv_rank + rot_dim]; o_lat (o_dt) [T, heads, kv_rank] */
 int tgis_k_latent_attn(const float* q_abs, const void* cache, int32_t dt, const int32_t* seqs_host, int32_t n_seqs,
-                       const int32_t* block_table_host, int32_t bt_rows, int32_t bt_stride, float* o_lat,
+                       const int32_t* block_table_host, int32_t bt_rows, int32_t bt_stride, void* o_lat, int32_t o_dt,
                        const tgis_k_latent_geom* g);
 int tgis_k_moe_route(const float* logits, int32_t ld, const float* bias, int32_t E, int32_t top, int32_t* ids, float* w,
                      float* side_gate, int32_t T);

@@ -88,17 +88,36 @@ def test_gemm_any_batched_heads_with_row_scale_and_mixed_types():
     assert torch.allclose(y.double().view(T, H, N), ref, rtol=1e-2, atol=2e-2)
 
 
+def test_gemm_any_tensor_core_variant_batched_and_long_k():
+    """bf16 operands with 16-byte aligned rows take the mma.sync kernel: several k-blocks with a ragged tail, several row and
+    column tiles, one problem per head, bf16 and fp32 outputs."""
+    T, H, K, N = 150, 3, 104, 136
+    g = torch.Generator().manual_seed(2)
+    x = _dev(torch.randn(T, H * K, generator=g), torch.bfloat16)
+    w = _dev(torch.randn(H, N, K, generator=g), torch.bfloat16)
+    scale = _dev(torch.rand(T, H, generator=g))
+    ref = torch.einsum("thk,hnk->thn", x.view(T, H, K).double(), w.double())
+    y = torch.full((T, H * N), float("nan"), device="cuda")
+    _gemm_any(x, w, y, T, N, K, ldx=H * K, ldw=K, ldy=H * N, batch=H, x_bs=K, w_bs=N * K, y_bs=N)
+    assert torch.allclose(y.double().view(T, H, N), ref, rtol=1e-5, atol=1e-3)
+    yb = torch.zeros(T, H * N, device="cuda", dtype=torch.bfloat16)
+    _gemm_any(x, w, yb, T, N, K, ldx=H * K, ldw=K, ldy=H * N, batch=H, x_bs=K, w_bs=N * K, y_bs=N, mode=2, row_scale=scale,
+              scale_ld=H)
+    assert torch.allclose(yb.double().view(T, H, N), ref * scale.double()[:, :, None], rtol=1e-2, atol=5e-2)
+
+
 @pytest.mark.parametrize("counts", [[0, 3, 0, 70, 1], [17], [1, 1, 1, 1]])
-def test_gemm_any_grouped_gather_swiglu(counts):
+@pytest.mark.parametrize("dt", [torch.float32, torch.bfloat16])
+def test_gemm_any_grouped_gather_swiglu(counts, dt):
     E, K, ff, top = len(counts), 24, 10, 2
     n = sum(counts)
     g = torch.Generator().manual_seed(n)
     tokens = (n + top - 1) // top
-    x = _dev(torch.randn(tokens, K, generator=g))
-    gate, up = torch.randn(E, ff, K, generator=g), torch.randn(E, ff, K, generator=g)
+    x = _dev(torch.randn(tokens, K, generator=g), dt)
+    gate, up = torch.randn(E, ff, K, generator=g).to(dt).float(), torch.randn(E, ff, K, generator=g).to(dt).float()
     w = torch.empty(E, 2 * ff, K)
     w[:, 0::2], w[:, 1::2] = gate, up                                  # interleaved rows: (gate_j, up_j)
-    w = _dev(w)
+    w = _dev(w, dt)
     seg = torch.tensor([0] + list(np.cumsum(counts)), dtype=torch.int32).cuda()
     order = torch.randperm(tokens * top, generator=g)[:n].to(torch.int32).cuda()   # position p reads token order[p] // top
     y = torch.full((n, ff), float("nan"), device="cuda")
@@ -193,7 +212,7 @@ def test_latent_prep_norms_rotary_cache_and_gates(rot_dim, rot_dims):
     # the query's rotated part lands behind the kv_rank absorbed entries of every head
     q = torch.randn(T, heads * (dim + rot_dim), generator=g)
     q_abs = torch.zeros(T, heads, row, device="cuda")
-    _ok(_lib().tgis_k_latent_q_rope(_p(_dev(q)), C.byref(geom), _p(_dev(pos, torch.int32)), _p(_cos_sin(n_pos, base, rot_dims)), _p(q_abs), T))
+    _ok(_lib().tgis_k_latent_q_rope(_p(_dev(q)), F32, C.byref(geom), _p(_dev(pos, torch.int32)), _p(_cos_sin(n_pos, base, rot_dims)), _p(q_abs), T))
     q_ref = O.rotate(q.double().view(T, heads, dim + rot_dim)[..., dim:], pos, base, rot_dims)
     assert torch.allclose(q_abs.cpu().double()[..., kv_rank:], q_ref, rtol=1e-5, atol=1e-5)
     assert bool((q_abs[..., :kv_rank] == 0).all())
@@ -238,7 +257,7 @@ def test_latent_attention_prompt_portion_and_decode_match_dense_softmax(heads, k
         o = torch.full((q_len, heads, kv_rank), float("nan"), device="cuda")
         seqs = (C.c_int32 * 4)(0, q_len, kv_len, 0)
         bt = (C.c_int32 * len(blocks))(*blocks.tolist())
-        _ok(_lib().tgis_k_latent_attn(_p(_dev(q_abs)), _p(cache), dt, seqs, 1, bt, 1, len(blocks), _p(o), C.byref(geom)))
+        _ok(_lib().tgis_k_latent_attn(_p(_dev(q_abs)), _p(cache), dt, seqs, 1, bt, 1, len(blocks), _p(o), F32, C.byref(geom)))
         ref = _attn_ref(q_abs, rows_seen, list(range(kv_len - q_len, kv_len)), window, scale, kv_rank)
         assert torch.allclose(o.cpu().double(), ref, rtol=2e-4, atol=2e-4), q_len
 
@@ -265,7 +284,7 @@ def test_latent_attention_one_key_decides_at_window_and_block_edges(q_len):
         q_abs[:, :, target] = 40.0
         o = torch.zeros(q_len, heads, kv_rank, device="cuda")
         seqs = (C.c_int32 * 4)(0, q_len, kv_len, 0)
-        _ok(_lib().tgis_k_latent_attn(_p(_dev(q_abs)), _p(cache), F32, seqs, 1, bt, 1, len(blocks), _p(o), C.byref(geom)))
+        _ok(_lib().tgis_k_latent_attn(_p(_dev(q_abs)), _p(cache), F32, seqs, 1, bt, 1, len(blocks), _p(o), F32, C.byref(geom)))
         o = o.cpu()
         for t in range(q_len):
             pq = first_q + t
@@ -412,6 +431,38 @@ def test_other_sizes_and_absent_parts(name):
     eng.close()
     assert _rel(got_whole, ref) < 3e-5
     assert _rel(np.concatenate(got), ref) < 3e-5
+
+
+def test_tensor_core_paths_agree_with_the_general_kernels(monkeypatch):
+    """Sizes that fit the tcgen05 kernel's operand layout (dense projections, shared expert, lm_head) and the mma.sync kernel
+    (per-head and per-expert products): the bf16 engine with and without the tcgen05 route, against the oracle."""
+    from oracle import ponenex_oracle as O
+    from vllm_tgis_adapter_b200.engine.ponenex import LayerSpec, synthetic_weights
+
+    b = dict(heads=4, dim=32, rot_dim=16, vdim=32, kv_rank=64, q_rank=128, window=50, rot_dims=16, rot_base=1000.0, scale=0.15,
+             experts=4, top=2, expert_ff=64, shared_ff=128)
+    mc = _config(layers=[LayerSpec(**b), LayerSpec(**{**b, "window": 200})], hidden=256, vocab=384, dtype="bfloat16")
+    weights = synthetic_weights(mc, 7)
+    toks = _tokens(300, 384, 8)
+    ref = O.forward(mc, weights, toks)
+    got = {}
+    for tc in ("1", "0"):
+        monkeypatch.setenv("TGIS_PNX_TC", tc)
+        eng = _engine(mc, weights, blocks=12)
+        whole = _whole(eng, toks)
+        parts, at = [], 0
+        for n in (257, 1, 1, 30, 2, 9):                       # a 257-token portion (two token tiles), then small steps
+            parts.append(eng.trace_step([("p", toks[at:at + n], list(range(n)))], ["p"] if at + n == len(toks) else []))
+            at += n
+        launches = eng.status().kernel_launches
+        eng.close()
+        got[tc] = (whole, np.concatenate(parts), launches)
+    for tc, (whole, parts, _) in got.items():
+        for out in (whole, parts):
+            rows = sorted(_rel(out[t:t + 1], ref[t:t + 1]) for t in range(len(toks)))
+            assert rows[len(rows) // 2] < 2e-2 and rows[int(0.8 * len(rows))] < 6e-2, (tc, rows[len(rows) // 2], rows[-1])
+    rows = sorted(_rel(got["1"][0][t:t + 1], torch.as_tensor(got["0"][0][t:t + 1]).double()) for t in range(len(toks)))
+    assert rows[len(rows) // 2] < 2e-2
 
 
 def test_prefill_portions_and_token_by_token_agree_with_whole_prompt():

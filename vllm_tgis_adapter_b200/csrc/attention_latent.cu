@@ -96,17 +96,22 @@ latent_prep_kernel(const float* __restrict__ y, int ldy, LatentGeom g, const flo
     st_any(cache, dtype, crow + g.kv_rank + j, rotary_entry(ykr, j, g.rot_dims, cs));
 }
 
-__global__ void latent_q_rope_kernel(const float* __restrict__ q, LatentGeom g, const int32_t* __restrict__ positions,
+template <class QT>
+__global__ void latent_q_rope_kernel(const QT* __restrict__ q, LatentGeom g, const int32_t* __restrict__ positions,
                                      const float* __restrict__ cos_sin, float* __restrict__ q_abs) {
   griddep_launch();
   griddep_wait();
   const int t = blockIdx.x;
   const float* cs = cos_sin + (size_t)positions[t] * g.rot_dims;
-  const int hd = g.dim + g.rot_dim, D = g.row();
+  const int hd = g.dim + g.rot_dim, D = g.row(), half = g.rot_dims / 2;
   for (int e = threadIdx.x; e < g.heads * g.rot_dim; e += blockDim.x) {
     const int h = e / g.rot_dim, j = e % g.rot_dim;
-    const float* v = q + ((size_t)t * g.heads + h) * hd + g.dim;
-    q_abs[((size_t)t * g.heads + h) * D + g.kv_rank + j] = rotary_entry(v, j, g.rot_dims, cs);
+    const QT* v = q + ((size_t)t * g.heads + h) * hd + g.dim;
+    float r;  // "rotate half" over the first rot_dims entries (rotary_entry, on the stored type)
+    if (j >= g.rot_dims) r = widen<QT>(v[j]);
+    else if (j < half) r = widen<QT>(v[j]) * cs[j] - widen<QT>(v[j + half]) * cs[half + j];
+    else r = widen<QT>(v[j]) * cs[j - half] + widen<QT>(v[j - half]) * cs[j];
+    q_abs[((size_t)t * g.heads + h) * D + g.kv_rank + j] = r;
   }
 }
 
@@ -115,7 +120,7 @@ template <class CT, int NACC>
 __global__ void __launch_bounds__(LAT_THREADS)
 latent_attn_kernel(const float* __restrict__ q_abs, const CT* __restrict__ cache, const AttnSeq* __restrict__ seqs,
                    const LatentTile* __restrict__ tiles, const int32_t* __restrict__ block_table, int bt_stride,
-                   float* __restrict__ o_lat, LatentGeom g) {
+                   void* __restrict__ o_lat, int o_dtype, LatentGeom g) {
   extern __shared__ __align__(16) float smem_f[];
   griddep_launch();
   griddep_wait();
@@ -203,19 +208,20 @@ latent_attn_kernel(const float* __restrict__ q_abs, const CT* __restrict__ cache
   for (int u = 0; u < 2; ++u) {
     if (!on[u]) continue;
     const int tq = pp[u] / nh, h = h0 + pp[u] % nh;
-    float* o = o_lat + ((size_t)(row0 + tq) * g.heads + h) * R;
+    const size_t o = ((size_t)(row0 + tq) * g.heads + h) * R;
     const float inv = 1.f / l[u];
 #pragma unroll
     for (int i = 0; i < NACC; ++i) {
       const int d = lane + 32 * i;
-      if (d < R) o[d] = acc[u][i] * inv;
+      if (d < R) st_any(o_lat, o_dtype, o + d, acc[u][i] * inv);
     }
   }
 }
 
 template <class CT, int NACC>
 cudaError_t launch_attn(const float* q_abs, const void* cache, const AttnSeq* seqs, const LatentTile* tiles, int n_tiles,
-                        const int32_t* block_table, int bt_stride, float* o_lat, const LatentGeom& g, cudaStream_t stream) {
+                        const int32_t* block_table, int bt_stride, void* o_lat, int o_dtype, const LatentGeom& g,
+                        cudaStream_t stream) {
   const int D = g.row();
   const size_t smem = ((size_t)KV_BLOCK * (D | 1) + (size_t)LATENT_PAIRS * D) * sizeof(float);
   if (smem > 200 * 1024) return cudaErrorInvalidValue;
@@ -228,16 +234,16 @@ cudaError_t launch_attn(const float* q_abs, const void* cache, const AttnSeq* se
   }
   const dim3 grid(n_tiles, (g.heads + LATENT_PAIRS - 1) / LATENT_PAIRS);
   return launch_k(latent_attn_kernel<CT, NACC>, grid, dim3(LAT_THREADS), smem, stream, q_abs,
-                  reinterpret_cast<const CT*>(cache), seqs, tiles, block_table, bt_stride, o_lat, g);
+                  reinterpret_cast<const CT*>(cache), seqs, tiles, block_table, bt_stride, o_lat, o_dtype, g);
 }
 
 template <class CT>
 cudaError_t launch_attn_ct(const float* q_abs, const void* cache, const AttnSeq* seqs, const LatentTile* tiles, int n_tiles,
-                           const int32_t* block_table, int bt_stride, float* o_lat, const LatentGeom& g,
+                           const int32_t* block_table, int bt_stride, void* o_lat, int o_dtype, const LatentGeom& g,
                            cudaStream_t stream) {
-  if (g.kv_rank <= 128) return launch_attn<CT, 4>(q_abs, cache, seqs, tiles, n_tiles, block_table, bt_stride, o_lat, g, stream);
-  if (g.kv_rank <= 256) return launch_attn<CT, 8>(q_abs, cache, seqs, tiles, n_tiles, block_table, bt_stride, o_lat, g, stream);
-  if (g.kv_rank <= 512) return launch_attn<CT, 16>(q_abs, cache, seqs, tiles, n_tiles, block_table, bt_stride, o_lat, g, stream);
+  if (g.kv_rank <= 128) return launch_attn<CT, 4>(q_abs, cache, seqs, tiles, n_tiles, block_table, bt_stride, o_lat, o_dtype, g, stream);
+  if (g.kv_rank <= 256) return launch_attn<CT, 8>(q_abs, cache, seqs, tiles, n_tiles, block_table, bt_stride, o_lat, o_dtype, g, stream);
+  if (g.kv_rank <= 512) return launch_attn<CT, 16>(q_abs, cache, seqs, tiles, n_tiles, block_table, bt_stride, o_lat, o_dtype, g, stream);
   return cudaErrorInvalidValue;
 }
 
@@ -252,19 +258,23 @@ cudaError_t latent_prep_launch(const float* y, int ldy, const LatentGeom& g, con
                   slot_mapping, cos_sin, cq, cache, dtype, gate);
 }
 
-cudaError_t latent_q_rope_launch(const float* q, const LatentGeom& g, const int32_t* positions, const float* cos_sin,
-                                 float* q_abs, int T, cudaStream_t stream) {
+cudaError_t latent_q_rope_launch(const void* q, int q_dtype, const LatentGeom& g, const int32_t* positions,
+                                 const float* cos_sin, float* q_abs, int T, cudaStream_t stream) {
   if (T <= 0) return cudaSuccess;
-  return launch_k(latent_q_rope_kernel, dim3(T), dim3(128), 0, stream, q, g, positions, cos_sin, q_abs);
+  if (q_dtype == DT_BF16)
+    return launch_k(latent_q_rope_kernel<__nv_bfloat16>, dim3(T), dim3(128), 0, stream,
+                    reinterpret_cast<const __nv_bfloat16*>(q), g, positions, cos_sin, q_abs);
+  return launch_k(latent_q_rope_kernel<float>, dim3(T), dim3(128), 0, stream, reinterpret_cast<const float*>(q), g, positions,
+                  cos_sin, q_abs);
 }
 
 cudaError_t latent_attn_launch(const float* q_abs, const void* cache, int dtype, const AttnSeq* seqs,
                                const LatentTile* tiles, int n_tiles, const int32_t* block_table, int bt_stride,
-                               float* o_lat, const LatentGeom& g, cudaStream_t stream) {
+                               void* o_lat, int o_dtype, const LatentGeom& g, cudaStream_t stream) {
   if (n_tiles <= 0) return cudaSuccess;
   if (dtype == DT_BF16)
-    return launch_attn_ct<__nv_bfloat16>(q_abs, cache, seqs, tiles, n_tiles, block_table, bt_stride, o_lat, g, stream);
-  return launch_attn_ct<float>(q_abs, cache, seqs, tiles, n_tiles, block_table, bt_stride, o_lat, g, stream);
+    return launch_attn_ct<__nv_bfloat16>(q_abs, cache, seqs, tiles, n_tiles, block_table, bt_stride, o_lat, o_dtype, g, stream);
+  return launch_attn_ct<float>(q_abs, cache, seqs, tiles, n_tiles, block_table, bt_stride, o_lat, o_dtype, g, stream);
 }
 
 }  // namespace tgis

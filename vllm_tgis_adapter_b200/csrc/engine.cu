@@ -257,8 +257,9 @@ struct tgis_engine {
   int pnx_dt = DT_BF16;                              // operand type of weights / matrix-product inputs / cache rows
   void *pnx_embed = nullptr, *pnx_head = nullptr, *pnx_hA = nullptr, *pnx_cq = nullptr, *pnx_oA = nullptr, *pnx_actS = nullptr,
        *pnx_actE = nullptr, *pnx_last = nullptr;
-  float *pnx_final_norm = nullptr, *pnx_resid = nullptr, *pnx_y1 = nullptr, *pnx_gate = nullptr, *pnx_q = nullptr,
-        *pnx_qabs = nullptr, *pnx_olat = nullptr, *pnx_o = nullptr, *pnx_rl = nullptr, *pnx_mixw = nullptr, *pnx_sgate = nullptr,
+  void *pnx_q = nullptr, *pnx_olat = nullptr;  // operand type: they feed the per-head products
+  float *pnx_final_norm = nullptr, *pnx_resid = nullptr, *pnx_y1 = nullptr, *pnx_gate = nullptr,
+        *pnx_qabs = nullptr, *pnx_o = nullptr, *pnx_rl = nullptr, *pnx_mixw = nullptr, *pnx_sgate = nullptr,
         *pnx_yS = nullptr, *pnx_yE = nullptr;
   int32_t *pnx_ids = nullptr, *pnx_segoff = nullptr, *pnx_order = nullptr, *pnx_inv = nullptr;
   int pnx_tile_tokens = 1, step_n_ltiles = 0;
@@ -1164,8 +1165,10 @@ struct tgis_engine {
 
   void init_pnx() {
     const tgis_config& c = cfg;
-    const size_t W = c.hidden, V = c.vocab, T = std::max(T_max, 16);
+    const size_t W = c.hidden, V = c.vocab, T = std::max(T_max, 256);
+    pnx_rows_alloc = T;
     pnx_dt = pnx_spec.dtype == TGIS_DTYPE_F32 ? DT_F32 : DT_BF16;
+    if (const char* e = getenv("TGIS_PNX_TC")) pnx_tc = atoi(e) != 0;
     if (const char* e = getenv("TGIS_DUMP_RESID")) pnx_dump_path = e;
     pnx_embed = pnx_alloc_dt(V * W);
     pnx_head = pnx_alloc_dt(V * W);
@@ -1221,9 +1224,9 @@ struct tgis_engine {
     pnx_y1 = pnx_alloc<float>(T * m_down);
     pnx_cq = pnx_alloc_dt(T * m_qr, true);
     pnx_gate = pnx_alloc<float>(T * m_heads);
-    pnx_q = pnx_alloc<float>(T * m_q);
+    pnx_q = pnx_alloc_dt(T * m_q, true);
     pnx_qabs = pnx_alloc<float>(T * m_qabs);
-    pnx_olat = pnx_alloc<float>(T * m_olat);
+    pnx_olat = pnx_alloc_dt(T * m_olat, true);
     pnx_oA = pnx_alloc_dt(T * m_ov, true);
     pnx_o = pnx_alloc<float>(T * W);
     pnx_rl = pnx_alloc<float>(T * m_E);
@@ -1237,7 +1240,7 @@ struct tgis_engine {
     pnx_yS = pnx_alloc<float>(T * W);
     pnx_actE = pnx_alloc_dt(T * m_top * m_ff, true);
     pnx_yE = pnx_alloc<float>(T * m_top * W);
-    pnx_last = pnx_alloc_dt((size_t)std::max(logit_rows_cap, 16) * W, true);
+    pnx_last = pnx_alloc_dt(std::max<size_t>(logit_rows_cap, T) * W, true);
     // paged cache of latent rows: the block ids of the engine's block manager index every layer's cache
     size_t kv_bytes = c.kv_cache_bytes;
     if (kv_bytes == 0) {
@@ -1334,9 +1337,40 @@ struct tgis_engine {
     return fail("unknown layer weight " + name);
   }
 
-  // Y = X W^T through the general kernel (dense)
+  // Dense Y = X W^T.  bf16 operands in the tcgen05 kernel's layout (whole 64-element k-blocks, at least one full weight tile)
+  // go to that kernel -- fp32 accumulators out, or SwiGLU fused over interleaved gate / up rows --, everything else to the
+  // general kernel.  Tensor maps are made on first use and kept (one per weight; one per activation buffer, width and
+  // token-tile height).  TGIS_PNX_TC=0: general kernel only.
+  std::unordered_map<const void*, CUtensorMap> pnx_wmaps;
+  std::unordered_map<uint64_t, CUtensorMap> pnx_xmaps;
+  bool pnx_tc = true;
+  size_t pnx_rows_alloc = 0;  // rows of every activation buffer (>= 256: a TMA box never leaves the allocation)
+  bool pnx_gemm_tc(const void* X, const void* Wt, void* Y, int ldy, int T, int N, int K, int out_mode) {
+    auto wit = pnx_wmaps.find(Wt);
+    if (wit == pnx_wmaps.end()) {
+      CUtensorMap m;
+      if (make_tmap_bf16_2d(&m, Wt, (uint64_t)N, (uint64_t)K, (uint64_t)K, 128, 64) != 0) return false;
+      wit = pnx_wmaps.emplace(Wt, m).first;
+    }
+    const int bi = bt_index(T);
+    const uint64_t xkey = (reinterpret_cast<uint64_t>(X) << 3) ^ ((uint64_t)K << 44) ^ (uint64_t)bi;
+    auto xit = pnx_xmaps.find(xkey);
+    if (xit == pnx_xmaps.end()) {
+      CUtensorMap m;
+      if (make_tmap_bf16_2d(&m, X, (uint64_t)pnx_rows_alloc, (uint64_t)K, (uint64_t)K, BT_VALUES[bi], 64) != 0) return false;
+      xit = pnx_xmaps.emplace(xkey, m).first;
+    }
+    CK(gemm_bf16_launch(wit->second, xit->second, Y, ldy, T, N, K, gemm_ws.p, gemm_counters.p, num_sms, stream, out_mode));
+    ++n_launches;
+    return true;
+  }
   void pnx_gemm(const void* X, int x_dt, int ldx, const void* Wt, void* Y, int y_dt, int ldy, int T, int N, int K,
-                int mode = GEMM_ANY_PLAIN) {
+                int mode = GEMM_ANY_PLAIN, bool x_tma_ok = true) {
+    if (pnx_tc && x_tma_ok && pnx_dt == DT_BF16 && x_dt == DT_BF16 && ldx == K && K % 64 == 0 && N % 8 == 0 && N >= 128 &&
+        !cfg.debug_gemm_ref) {
+      const int out_mode = mode == GEMM_ANY_SWIGLU && y_dt == DT_BF16 ? 2 : mode == GEMM_ANY_PLAIN ? (y_dt == DT_F32 ? 1 : 0) : -1;
+      if (out_mode >= 0 && pnx_gemm_tc(X, Wt, Y, ldy, T, N, K, out_mode)) return;
+    }
     GemmAny a{};
     a.X = X; a.W = Wt; a.Y = Y;
     a.x_dtype = x_dt; a.w_dtype = pnx_dt; a.y_dtype = y_dt;
@@ -1370,21 +1404,21 @@ struct tgis_engine {
       pnx_gemm(pnx_hA, A, W, l.w_down, pnx_y1, DT_F32, l.n_down(), T, l.n_down(), W);
       CK(latent_prep_launch(pnx_y1, l.n_down(), g, l.qnorm, l.kvnorm, eps, d_pos, d_slot, l.cos_sin, pnx_cq, l.cache, A,
                             pnx_gate, T, stream));
-      pnx_gemm(pnx_cq, A, s.q_rank, l.w_uq, pnx_q, DT_F32, H * hd, T, H * hd, s.q_rank);
-      CK(latent_q_rope_launch(pnx_q, g, d_pos, l.cos_sin, pnx_qabs, T, stream));
+      pnx_gemm(pnx_cq, A, s.q_rank, l.w_uq, pnx_q, A, H * hd, T, H * hd, s.q_rank);
+      CK(latent_q_rope_launch(pnx_q, A, g, d_pos, l.cos_sin, pnx_qabs, T, stream));
       {  // q_abs_h = W_uk,h^T q_nope_h  (one problem per head)
         GemmAny a{};
         a.X = pnx_q; a.W = l.w_ukT; a.Y = pnx_qabs;
-        a.x_dtype = DT_F32; a.w_dtype = A; a.y_dtype = DT_F32;
+        a.x_dtype = A; a.w_dtype = A; a.y_dtype = DT_F32;
         a.T = T; a.N = s.kv_rank; a.K = s.dim; a.ldx = H * hd; a.ldw = s.dim; a.ldy = H * D;
         a.batch = H; a.x_bs = hd; a.w_bs = (long long)s.kv_rank * s.dim; a.y_bs = D;
         CK(gemm_any_launch(a, stream));
       }
-      CK(latent_attn_launch(pnx_qabs, l.cache, A, d_seqs, d_tiles, step_n_ltiles, d_bt, bt_stride, pnx_olat, g, stream));
+      CK(latent_attn_launch(pnx_qabs, l.cache, A, d_seqs, d_tiles, step_n_ltiles, d_bt, bt_stride, pnx_olat, A, g, stream));
       {  // o_h = gate_h * W_uv,h o_lat_h
         GemmAny a{};
         a.X = pnx_olat; a.W = l.w_uv; a.Y = pnx_oA;
-        a.x_dtype = DT_F32; a.w_dtype = A; a.y_dtype = A;
+        a.x_dtype = A; a.w_dtype = A; a.y_dtype = A;
         a.T = T; a.N = s.vdim; a.K = s.kv_rank; a.ldx = H * s.kv_rank; a.ldw = s.kv_rank; a.ldy = H * s.vdim;
         a.batch = H; a.x_bs = s.kv_rank; a.w_bs = (long long)s.vdim * s.kv_rank; a.y_bs = s.vdim;
         a.mode = GEMM_ANY_ROWSCALE; a.row_scale = pnx_gate; a.scale_ld = H;

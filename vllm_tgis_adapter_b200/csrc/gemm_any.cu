@@ -10,8 +10,13 @@
 // Every output element is the sum over k = 0 .. K-1 in ascending order inside one thread, so a row's result depends
 // neither on the other rows of the launch nor on where in a segment it landed.
 //
-// The math runs on the FMA pipe (a [16 TM x 64] tile per 256-thread CTA, TM x 4 outputs per thread, k-blocks of 16
-// staged through shared memory).  Launches that fit the tcgen05 kernel's operand layout are routed there by the engine.
+// Two kernels: bf16 operands whose rows start on 16-byte boundaries run on the tensor cores (gemm_any_mma_kernel below);
+// everything else -- fp32 operands, odd leading dimensions -- runs on the FMA pipe (a [16 TM x 64] tile per 256-thread CTA,
+// TM x 4 outputs per thread, k-blocks of 16 staged through shared memory).  Dense launches that fit the tcgen05 kernel's
+// operand layout are routed there by the engine.
+#include <cstdint>
+#include <cstdlib>
+
 #include "kernels.h"
 #include "launch.cuh"
 #include "ptx.cuh"
@@ -134,6 +139,163 @@ __global__ void __launch_bounds__(ANY_THREADS) gemm_any_kernel(GemmAny a) {
   }
 }
 
+// ---- tensor-core variant (bf16 operands, 16-byte aligned rows): mma.sync m16n8k16, fp32 accumulators ---------------
+// CTA tile 64 rows x 128 weight rows, k-blocks of 32 double-buffered with cp.async (out-of-range rows and the k tail are
+// zero-filled by the copy), 8 warps as 2 x 4, warp tile 32 x 32; operands reach the registers through ldmatrix from rows
+// padded to 80 bytes (conflict-free).  Same geometries and epilogues as the FMA kernel; the k order inside an output
+// element is fixed (ascending k-blocks, the MMA's own order inside), so a row's result does not depend on its neighbours.
+constexpr int MMA_BM = 64, MMA_BN = 128, MMA_BK = 32, MMA_LD = MMA_BK + 8;
+
+__device__ __forceinline__ void cp_async_16(void* smem, const void* gmem, bool valid) {
+  const uint32_t s = (uint32_t)__cvta_generic_to_shared(smem);
+  const int bytes = valid ? 16 : 0;
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;\n" ::"r"(s), "l"(gmem), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;\n" ::: "memory"); }
+template <int N>
+__device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;\n" ::"n"(N) : "memory"); }
+__device__ __forceinline__ void ldsm_x4(uint32_t (&r)[4], const void* smem) {
+  const uint32_t s = (uint32_t)__cvta_generic_to_shared(smem);
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];\n"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(s));
+}
+__device__ __forceinline__ void mma_bf16_16816(float (&c)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
+  asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};\n"
+               : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+               : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+
+template <class OT>
+__global__ void __launch_bounds__(ANY_THREADS) gemm_any_mma_kernel(GemmAny a) {
+  using bf = __nv_bfloat16;
+  __shared__ __align__(16) bf Xs[2][MMA_BM][MMA_LD];
+  __shared__ __align__(16) bf Ws[2][MMA_BN][MMA_LD];
+  __shared__ int row_src[MMA_BM], row_dst[MMA_BM];
+  griddep_launch();
+  griddep_wait();
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  int row0, row_end, group = 0;
+  if (a.seg_off != nullptr) {
+    int t = blockIdx.y;
+    for (; group < a.n_groups; ++group) {
+      const int cnt = a.seg_off[group + 1] - a.seg_off[group];
+      const int nt = (cnt + MMA_BM - 1) / MMA_BM;
+      if (t < nt) break;
+      t -= nt;
+    }
+    if (group >= a.n_groups) return;
+    row0 = a.seg_off[group] + t * MMA_BM;
+    row_end = a.seg_off[group + 1];
+  } else {
+    row0 = blockIdx.y * MMA_BM;
+    row_end = a.T;
+  }
+  if (tid < MMA_BM) {
+    const int r = row0 + tid;
+    row_src[tid] = r < row_end ? (a.gather != nullptr ? a.gather[r] / a.gather_div : r) : -1;
+    row_dst[tid] = r < row_end ? r : -1;
+  }
+  __syncthreads();
+  const int z = blockIdx.z;
+  const bf* X = reinterpret_cast<const bf*>(a.X) + (size_t)z * a.x_bs;
+  const bf* W = reinterpret_cast<const bf*>(a.W) + (size_t)z * a.w_bs + (size_t)group * a.w_gs;
+  OT* Y = reinterpret_cast<OT*>(a.Y) + (size_t)z * a.y_bs;
+  const int n0 = blockIdx.x * MMA_BN;
+  const int wm = warp >> 2, wn = warp & 3;  // 2 x 4 warps
+
+  auto stage_load = [&](int st, int k0) {
+    {  // X: 64 rows x 4 chunks of 8 elements
+      const int r = tid >> 2, c = tid & 3;
+      const int src = row_src[r];
+      const bool ok = src >= 0 && k0 + c * 8 < a.K;
+      cp_async_16(&Xs[st][r][c * 8], ok ? X + (size_t)src * a.ldx + k0 + c * 8 : X, ok);
+    }
+#pragma unroll
+    for (int i = 0; i < 2; ++i) {  // W: 128 rows x 4 chunks
+      const int id = tid + i * ANY_THREADS;
+      const int n = id >> 2, c = id & 3;
+      const bool ok = n0 + n < a.N && k0 + c * 8 < a.K;
+      cp_async_16(&Ws[st][n][c * 8], ok ? W + (size_t)(n0 + n) * a.ldw + k0 + c * 8 : W, ok);
+    }
+    cp_async_commit();
+  };
+
+  float acc[2][4][4];
+#pragma unroll
+  for (int i = 0; i < 2; ++i)
+#pragma unroll
+    for (int j = 0; j < 4; ++j)
+#pragma unroll
+      for (int e = 0; e < 4; ++e) acc[i][j][e] = 0.f;
+
+  const int KB = (a.K + MMA_BK - 1) / MMA_BK;
+  stage_load(0, 0);
+  for (int kb = 0; kb < KB; ++kb) {
+    const int st = kb & 1;
+    if (kb + 1 < KB) {
+      stage_load(st ^ 1, (kb + 1) * MMA_BK);
+      cp_async_wait<1>();
+    } else {
+      cp_async_wait<0>();
+    }
+    __syncthreads();
+#pragma unroll
+    for (int ks = 0; ks < MMA_BK / 16; ++ks) {
+      uint32_t af[2][4], bfr[2][4];
+#pragma unroll
+      for (int mi = 0; mi < 2; ++mi) ldsm_x4(af[mi], &Xs[st][wm * 32 + mi * 16 + (lane & 15)][ks * 16 + (lane >> 4) * 8]);
+#pragma unroll
+      for (int nj = 0; nj < 2; ++nj)
+        ldsm_x4(bfr[nj], &Ws[st][wn * 32 + nj * 16 + (lane >> 4) * 8 + (lane & 7)][ks * 16 + ((lane >> 3) & 1) * 8]);
+#pragma unroll
+      for (int mi = 0; mi < 2; ++mi)
+#pragma unroll
+        for (int ni = 0; ni < 4; ++ni) mma_bf16_16816(acc[mi][ni], af[mi], bfr[ni >> 1][(ni & 1) * 2], bfr[ni >> 1][(ni & 1) * 2 + 1]);
+    }
+    __syncthreads();
+  }
+  // ---- epilogue: a thread holds columns (2t, 2t + 1) of rows g and g + 8 of every 16 x 8 block
+  const int g = lane >> 2, t2 = (lane & 3) * 2;
+#pragma unroll
+  for (int mi = 0; mi < 2; ++mi)
+#pragma unroll
+    for (int half = 0; half < 2; ++half) {
+      const int dst = row_dst[wm * 32 + mi * 16 + g + half * 8];
+      if (dst < 0) continue;
+      const float s = a.mode == GEMM_ANY_ROWSCALE ? a.row_scale[(size_t)dst * a.scale_ld + z] : 1.f;
+#pragma unroll
+      for (int ni = 0; ni < 4; ++ni) {
+        const int n = n0 + wn * 32 + ni * 8 + t2;
+        const float v0 = acc[mi][ni][half * 2], v1 = acc[mi][ni][half * 2 + 1];
+        if (a.mode == GEMM_ANY_SWIGLU) {
+          if (n + 1 < a.N) st_from_float(Y + (size_t)dst * a.ldy + n / 2, v0 / (1.f + expf(-v0)) * v1);
+        } else {
+          if (n < a.N) st_from_float(Y + (size_t)dst * a.ldy + n, v0 * s);
+          if (n + 1 < a.N) st_from_float(Y + (size_t)dst * a.ldy + n + 1, v1 * s);
+        }
+      }
+    }
+}
+
+template <class OT>
+cudaError_t launch_mma(const GemmAny& a, cudaStream_t stream) {
+  const int row_tiles = a.seg_off != nullptr ? (a.T + MMA_BM - 1) / MMA_BM + a.n_groups : (a.T + MMA_BM - 1) / MMA_BM;
+  const dim3 grid((a.N + MMA_BN - 1) / MMA_BN, row_tiles, a.batch > 0 ? a.batch : 1);
+  if (grid.y > 65535 || grid.z > 65535) return cudaErrorInvalidValue;
+  return launch_k(gemm_any_mma_kernel<OT>, grid, dim3(ANY_THREADS), 0, stream, a);
+}
+
+bool mma_eligible(const GemmAny& a) {
+  static int on = -1;
+  if (on < 0) {
+    const char* e = getenv("TGIS_GEMM_ANY_MMA");
+    on = (e && e[0] == '0') ? 0 : 1;
+  }
+  auto al16 = [](const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; };
+  return on && a.x_dtype == DT_BF16 && a.w_dtype == DT_BF16 && a.K % 8 == 0 && a.ldx % 8 == 0 && a.ldw % 8 == 0 &&
+         a.x_bs % 8 == 0 && a.w_bs % 8 == 0 && a.w_gs % 8 == 0 && al16(a.X) && al16(a.W);
+}
+
 template <class XT, class WT, class OT>
 cudaError_t launch_tm(const GemmAny& a, cudaStream_t stream) {
   // rows per tile: 16 for skinny problems (decode steps, small expert segments), 64 otherwise
@@ -155,6 +317,7 @@ cudaError_t gemm_any_launch(const GemmAny& a, cudaStream_t stream) {
   if (a.mode == GEMM_ANY_ROWSCALE && a.row_scale == nullptr) return cudaErrorInvalidValue;
   if (a.gather != nullptr && a.gather_div <= 0) return cudaErrorInvalidValue;
   using bf = __nv_bfloat16;
+  if (mma_eligible(a)) return a.y_dtype == DT_BF16 ? launch_mma<bf>(a, stream) : launch_mma<float>(a, stream);
   const int key = a.x_dtype * 4 + a.w_dtype * 2 + a.y_dtype;  // DT_F32 = 0, DT_BF16 = 1
   switch (key) {
     case 0: return launch_tm<float, float, float>(a, stream);

@@ -303,19 +303,19 @@ struct LatentGeom {
 cudaError_t latent_prep_launch(const float* y, int ldy, const LatentGeom& g, const float* w_q, const float* w_kv, float eps,
                                const int32_t* positions, const int32_t* slot_mapping, const float* cos_sin, void* cq,
                                void* cache, int dtype, float* gate, int T, cudaStream_t stream);
-// q [T, heads * (dim + rot_dim)] fp32 -> q_abs[t, h, kv_rank ..] = rotary(q_rot_h, pos[t])   (the first kv_rank entries of
+// q [T, heads * (dim + rot_dim)] DT_* -> q_abs[t, h, kv_rank ..] = rotary(q_rot_h, pos[t])   (the first kv_rank entries of
 // every head are written by the absorbing batched product)
-cudaError_t latent_q_rope_launch(const float* q, const LatentGeom& g, const int32_t* positions, const float* cos_sin,
-                                 float* q_abs, int T, cudaStream_t stream);
+cudaError_t latent_q_rope_launch(const void* q, int q_dtype, const LatentGeom& g, const int32_t* positions,
+                                 const float* cos_sin, float* q_abs, int T, cudaStream_t stream);
 struct LatentTile {  // one CTA's queries: tokens [q0, q0 + nq) of the step's sequence `seq` (device array)
   int32_t seq, q0, nq, pad;
 };
 constexpr int LATENT_PAIRS = 16;  // (token, head) pairs per CTA
 inline int latent_tile_tokens(int heads) { return heads >= LATENT_PAIRS ? 1 : LATENT_PAIRS / heads; }
-// q_abs fp32 [T, heads, row()], cache DT_* [num_blocks][KV_BLOCK][row()], o_lat fp32 [T, heads, kv_rank]
+// q_abs fp32 [T, heads, row()], cache DT_* [num_blocks][KV_BLOCK][row()], o_lat DT_* [T, heads, kv_rank]
 cudaError_t latent_attn_launch(const float* q_abs, const void* cache, int dtype, const AttnSeq* seqs,
                                const LatentTile* tiles, int n_tiles, const int32_t* block_table, int bt_stride,
-                               float* o_lat, const LatentGeom& g, cudaStream_t stream);
+                               void* o_lat, int o_dtype, const LatentGeom& g, cudaStream_t stream);
 
 // ---- moe.cu: top-k router and the bookkeeping of the grouped expert products ----------------------------------------
 // logits fp32 [T, ld] (columns [0, E): experts; column E, when side_gate != nullptr: the shared expert's gate logit):

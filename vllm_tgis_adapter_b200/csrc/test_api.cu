@@ -558,15 +558,15 @@ int tgis_k_latent_prep(const float* y, int32_t ldy, const tgis_k_latent_geom* g,
   return 0;
 }
 
-int tgis_k_latent_q_rope(const float* q, const tgis_k_latent_geom* g, const int32_t* positions, const float* cos_sin,
-                         float* q_abs, int32_t T) {
-  KCK(latent_q_rope_launch(q, to_geom(g), positions, cos_sin, q_abs, T, 0));
+int tgis_k_latent_q_rope(const void* q, int32_t q_dt, const tgis_k_latent_geom* g, const int32_t* positions,
+                         const float* cos_sin, float* q_abs, int32_t T) {
+  KCK(latent_q_rope_launch(q, q_dt, to_geom(g), positions, cos_sin, q_abs, T, 0));
   KCK(cudaDeviceSynchronize());
   return 0;
 }
 
 int tgis_k_latent_attn(const float* q_abs, const void* cache, int32_t dt, const int32_t* seqs_host, int32_t n_seqs,
-                       const int32_t* block_table_host, int32_t bt_rows, int32_t bt_stride, float* o_lat,
+                       const int32_t* block_table_host, int32_t bt_rows, int32_t bt_stride, void* o_lat, int32_t o_dt,
                        const tgis_k_latent_geom* g) {
   const LatentGeom geom = to_geom(g);
   std::vector<AttnSeq> seqs(n_seqs);
@@ -582,7 +582,7 @@ int tgis_k_latent_attn(const float* q_abs, const void* cache, int32_t dt, const 
   KCK(d_seqs.upload(seqs.data(), seqs.size()));
   KCK(d_tiles.upload(tiles.data(), tiles.size()));
   KCK(d_bt.upload(block_table_host, (size_t)bt_rows * bt_stride));
-  KCK(latent_attn_launch(q_abs, cache, dt, d_seqs.p, d_tiles.p, (int)tiles.size(), d_bt.p, bt_stride, o_lat, geom, 0));
+  KCK(latent_attn_launch(q_abs, cache, dt, d_seqs.p, d_tiles.p, (int)tiles.size(), d_bt.p, bt_stride, o_lat, o_dt, geom, 0));
   KCK(cudaDeviceSynchronize());
   return 0;
 }

@@ -183,8 +183,8 @@ def load_library() -> C.CDLL:
     lib.tgis_k_rmsnorm_f32.argtypes = [vp, i32, vp, f32, vp, i32, i32, i32, i32, f32]
     lib.tgis_k_resid_tail.argtypes = [vp, vp, vp, vp, i32, vp, vp, vp, vp, vp, vp, i32, f32, f32, f32, i32, i32]
     lib.tgis_k_latent_prep.argtypes = [vp, i32, gp, vp, vp, f32, vp, vp, vp, vp, vp, i32, vp, i32]
-    lib.tgis_k_latent_q_rope.argtypes = [vp, gp, vp, vp, vp, i32]
-    lib.tgis_k_latent_attn.argtypes = [vp, vp, i32, C.POINTER(i32), i32, C.POINTER(i32), i32, i32, vp, gp]
+    lib.tgis_k_latent_q_rope.argtypes = [vp, i32, gp, vp, vp, vp, i32]
+    lib.tgis_k_latent_attn.argtypes = [vp, vp, i32, C.POINTER(i32), i32, C.POINTER(i32), i32, i32, vp, i32, gp]
     lib.tgis_k_moe_route.argtypes = [vp, i32, vp, i32, i32, vp, vp, vp, i32]
     lib.tgis_k_moe_align.argtypes = [vp, i32, i32, i32, vp, vp, vp]
     _LIB = lib
