@@ -62,6 +62,10 @@ def parse_args():
                          "online-serving default")
     ap.add_argument("--sampling", default="greedy", choices=["greedy", "cfg3"],
                     help="cfg3 = repetition penalty 1.2 + length penalty (64, 1.05) + typical_p 0.9 sampling")
+    ap.add_argument("--arch-compare", action="store_true",
+                    help="instead of the default workload: prefill / decode throughput of the Ponenex sizes beside Llama "
+                         "stacks of equal hidden size, depth and active feed-forward width (--batch, --prompt-len, --gen-len)")
+    ap.add_argument("--arch-sizes", default="", help="--arch-compare: only these presets (comma separated)")
     ap.add_argument("--layers", type=int, default=0, help="experiments: override the preset's layer count")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--cpu-layers", type=int, default=8, help="layers timed by the CPU baseline (extrapolated)")
@@ -765,8 +769,101 @@ def run_ours(args) -> dict | None:
     return out
 
 
+# ------------------------------------------------------------------------------------------------ --arch-compare
+# Prefill and decode throughput of the Ponenex family beside the closest existing family (Llama) at equal hidden size, layer
+# count and active feed-forward width, random weights, device-timed (the engine's CUDA events around every step).  Not the
+# default workload: `python bench.py --arch-compare` prints its own JSON line and leaves the contract line alone.
+ARCH_COMPARE = [("ponenex-1k", "llama-cmp-1k"), ("ponenex-2k", "llama-cmp-2k")]
+
+
+def _arch_work(mc, B: int, ctx: float) -> tuple[float, float]:
+    """(matrix-product FLOPs per token incl. attention at context `ctx`, weight + cache bytes one decode step of batch B
+    streams) -- the numerators of the two rooflines."""
+    h, v = mc.hidden, mc.vocab
+    if mc.arch == "ponenex":
+        flops = bytes_ = 0.0
+        for l in mc.layers:
+            row, keys = l.kv_rank + l.rot_dim, min(ctx, l.window or ctx)
+            dense = h * (l.q_rank + row + l.heads) + l.q_rank * l.heads * (l.dim + l.rot_dim) + l.heads * l.vdim * h
+            per_head = l.heads * (l.dim * l.kv_rank + l.kv_rank * l.vdim)
+            attn = l.heads * keys * (row + l.kv_rank)
+            ff_tok = 3 * h * (l.top * l.expert_ff + l.shared_ff) + h * (l.experts + 1)
+            flops += 2.0 * (dense + per_head + attn + ff_tok)
+            experts_touched = min(l.experts, B * l.top)
+            bytes_ += 2.0 * (dense + per_head + 3 * h * (experts_touched * l.expert_ff + l.shared_ff) + h * (l.experts + 1))
+            bytes_ += 2.0 * B * keys * row
+        return flops + 2.0 * h * v, bytes_ + 2.0 * h * v
+    qd, kvd = mc.n_q_heads * 128, mc.n_kv_heads * 128
+    per_layer = h * (qd + 2 * kvd) + qd * h + 3 * h * mc.ffn
+    flops = mc.n_layers * 2.0 * (per_layer + mc.n_q_heads * ctx * 2 * 128) + 2.0 * h * v
+    bytes_ = mc.n_layers * 2.0 * (per_layer + B * ctx * 2 * kvd) + 2.0 * h * v
+    return flops, bytes_
+
+
+def run_arch_compare(args) -> None:
+    import dataclasses
+
+    import torch
+
+    from vllm_tgis_adapter_b200.engine.core import PRESETS, NativeEngine, cache_block_bytes, make_sampling_params
+    from vllm_tgis_adapter_b200.engine.loader import load_synthetic_weights, rope_cos_sin
+    from vllm_tgis_adapter_b200.engine.ponenex import PRESETS as PNX
+
+    torch.cuda.set_device(0)
+    hbm_gbs, _ = peaks()
+    try:
+        tf = float(json.loads((ROOT / "MEASURED_PEAKS.json").read_text())["bf16_tflops_sustained"])
+    except (OSError, KeyError, ValueError):
+        tf = 1400.0
+    B, P, G = args.batch, args.prompt_len, args.gen_len
+    rows = []
+    for pair in ARCH_COMPARE:
+        if args.arch_sizes and not any(m in args.arch_sizes.split(",") for m in pair):
+            continue
+        for name in pair:
+            mc = dataclasses.replace(PNX.get(name) or PRESETS[name], max_model_len=P + G + 64)
+            blocks = B * ((P + G + 31) // 32 + 1)
+            eng = NativeEngine(mc, max_num_seqs=B, max_batched_tokens=args.max_batched_tokens,
+                               kv_cache_bytes=int(cache_block_bytes(mc) * blocks * 1.05), seed=1)
+            load_synthetic_weights(eng, mc, 7, 0)
+            if mc.arch == "llama":
+                eng.load_weight("tgis.rope_cos_sin", rope_cos_sin(mc))
+            torch.cuda.synchronize()
+            torch.cuda.empty_cache()
+            gen = torch.Generator().manual_seed(11)
+            prompts = [torch.randint(3, mc.vocab, (P,), generator=gen).tolist() for _ in range(B)]
+            sp = make_sampling_params(greedy=True, max_tokens=G, min_tokens=G, eos_token_id=2)
+            for _ in range(max(args.warmup, 1)):
+                _job(eng, prompts, sp)
+            st0 = eng.status()
+            with ClockSampler(0) as cs:
+                for _ in range(args.steps):
+                    _job(eng, prompts, sp)
+            st1 = eng.status()
+            eng.close()
+            dec_ms, dec_tok = st1.gpu_decode_ms - st0.gpu_decode_ms, st1.decode_tokens - st0.decode_tokens
+            pre_ms, pre_tok = st1.gpu_mixed_ms - st0.gpu_mixed_ms, args.steps * B * P
+            flops_tok, step_bytes = _arch_work(mc, B, P + G / 2)
+            flops_pre, _ = _arch_work(mc, B, P / 2)
+            dec_step_ms = dec_ms / max(st1.decode_steps - st0.decode_steps, 1)
+            row = {"model": name, "arch": mc.arch, "batch": B, "prompt_len": P, "gen_len": G,
+                   "prefill_tokens_per_s": round(pre_tok / (pre_ms * 1e-3)), "decode_tokens_per_s": round(dec_tok / (dec_ms * 1e-3)),
+                   "decode_ms_per_step": round(dec_step_ms, 3),
+                   "prefill_frac_of_measured_bf16": round(flops_pre * pre_tok / (pre_ms * 1e-3) / (tf * 1e12), 4),
+                   "decode_frac_of_measured_hbm": round(step_bytes / (dec_step_ms * 1e-3) / (hbm_gbs * 1e9), 4),
+                   "launches_per_decode_step": round((st1.kernel_launches - st0.kernel_launches) / max(st1.steps - st0.steps, 1)),
+                   "clocks": cs.summary()}
+            log(f"arch-compare {row}")
+            rows.append(row)
+    print(json.dumps({"arch_compare": rows, "data": "synthetic", "dtype": "bf16",
+                      "denominators": {"hbm_gbs_measured": hbm_gbs, "bf16_tflops_sustained_measured": tf}}), flush=True)
+
+
 def main():
     args = parse_args()
+    if args.arch_compare:
+        run_arch_compare(args)
+        return
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
     if args.impl == "reference":

@@ -241,11 +241,13 @@ def _paged(rows, n_blocks_pool, seed, dt):
     return cache.to(dt).cuda().contiguous(), blocks.to(torch.int32)
 
 
-@pytest.mark.parametrize("heads,kv_rank,rot_dim", [(6, 24, 8), (1, 130, 2), (20, 40, 6), (3, 300, 4)])
+@pytest.mark.parametrize("heads,kv_rank,rot_dim", [(6, 24, 8), (1, 130, 2), (20, 40, 6), (3, 300, 4), (16, 512, 64), (5, 72, 8),
+                                                   (2, 128, 32)])
 @pytest.mark.parametrize("dt", [F32, BF16])
 def test_latent_attention_prompt_portion_and_decode_match_dense_softmax(heads, kv_rank, rot_dim, dt):
-    window, scale, kv_len = 45, 0.3, 150
+    window, kv_len = 45, 150
     D = kv_rank + rot_dim
+    scale = 2.0 / math.sqrt(D)                 # scores of spread 2 whatever the row length
     g = torch.Generator().manual_seed(heads)
     rows = torch.randn(kv_len, D, generator=g)
     cache, blocks = _paged(rows, 9, heads, _tdt(dt))
@@ -259,7 +261,8 @@ def test_latent_attention_prompt_portion_and_decode_match_dense_softmax(heads, k
         bt = (C.c_int32 * len(blocks))(*blocks.tolist())
         _ok(_lib().tgis_k_latent_attn(_p(_dev(q_abs)), _p(cache), dt, seqs, 1, bt, 1, len(blocks), _p(o), F32, C.byref(geom)))
         ref = _attn_ref(q_abs, rows_seen, list(range(kv_len - q_len, kv_len)), window, scale, kv_rank)
-        assert torch.allclose(o.cpu().double(), ref, rtol=2e-4, atol=2e-4), q_len
+        tol = 2e-4 if dt == F32 else 3e-2    # bf16 rows with aligned sizes run on the tensor cores: Q and P rounded to bf16
+        assert torch.allclose(o.cpu().double(), ref, rtol=tol, atol=tol), q_len
 
 
 @pytest.mark.parametrize("q_len", [1, 5, 64])

@@ -11,6 +11,8 @@
 // against it: lane = key for the scores, lane = latent dimension (strided by 32) for the weighted sum.  A query's
 // arithmetic depends only on its own position and on the block grid of its sequence, not on the tile or step it came in.
 #include <cfloat>
+#include <cstdint>
+#include <cstdlib>
 
 #include "kernels.h"
 #include "launch.cuh"
@@ -218,6 +220,221 @@ latent_attn_kernel(const float* __restrict__ q_abs, const CT* __restrict__ cache
   }
 }
 
+// ---- tensor-core variant (bf16 cache rows of a multiple of 8 entries) ------------------------------------------------
+// Same work split as latent_attn_kernel (a CTA = up to 16 (token, head) pairs of one sequence against the 32-row cache
+// blocks they can see), with the two products on mma.sync m16n8k16: the 16 pairs are the M rows of both.
+//   scores  S [16 x 32] = Q [16 x D] K^T: the row length D is cut in two halves over the warps (warps 0-3 / 4-7), each warp
+//           takes 8 keys; the two fp32 partial tiles meet in shared memory
+//   softmax fp32, one warp per two rows, lane = key (as in the FMA kernel): running maximum and sum, P rounded to bf16
+//   output  O [16 x kv_rank] += P [16 x 32] C [32 x kv_rank]: warp w owns the 8-column tiles w, w + 8, ... (fp32 accumulators
+//           in registers for the whole walk), C read straight from the staged rows with ldmatrix.trans
+// Cache blocks arrive by cp.async, double-buffered: block i + 1 lands while block i is being used.  Q is scaled and rounded
+// to bf16 once.  A query's arithmetic still depends only on its own position and its sequence's block grid.
+__device__ __forceinline__ void lat_cp_async_16(void* smem, const void* gmem) {
+  const uint32_t s = (uint32_t)__cvta_generic_to_shared(smem);
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16;\n" ::"r"(s), "l"(gmem) : "memory");
+}
+__device__ __forceinline__ void lat_ldsm_x4(uint32_t (&r)[4], const void* smem) {
+  const uint32_t s = (uint32_t)__cvta_generic_to_shared(smem);
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];\n"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(s));
+}
+__device__ __forceinline__ void lat_ldsm_x2(uint32_t (&r)[2], const void* smem) {
+  const uint32_t s = (uint32_t)__cvta_generic_to_shared(smem);
+  asm volatile("ldmatrix.sync.aligned.m8n8.x2.shared.b16 {%0,%1}, [%2];\n" : "=r"(r[0]), "=r"(r[1]) : "r"(s));
+}
+__device__ __forceinline__ void lat_ldsm_x4_trans(uint32_t (&r)[4], const void* smem) {
+  const uint32_t s = (uint32_t)__cvta_generic_to_shared(smem);
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];\n"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(s));
+}
+__device__ __forceinline__ void lat_mma(float (&c)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
+  asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};\n"
+               : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+               : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+inline __host__ __device__ int lat_ldq(int D) { return (D + 15) / 16 * 16 + 8; }  // padded row length (bf16 elements)
+inline size_t lat_mma_smem(int D) {
+  return (size_t)(LATENT_PAIRS + 2 * KV_BLOCK) * lat_ldq(D) * 2 + (size_t)2 * LATENT_PAIRS * 33 * 4 + LATENT_PAIRS * 40 * 2 +
+         2 * LATENT_PAIRS * 4;
+}
+
+template <int NT>  // NT * 64 >= kv_rank
+__global__ void __launch_bounds__(LAT_THREADS)
+latent_attn_mma_kernel(const float* __restrict__ q_abs, const __nv_bfloat16* __restrict__ cache,
+                       const AttnSeq* __restrict__ seqs, const LatentTile* __restrict__ tiles,
+                       const int32_t* __restrict__ block_table, int bt_stride, void* __restrict__ o_lat, int o_dtype,
+                       LatentGeom g) {
+  using bf = __nv_bfloat16;
+  extern __shared__ __align__(16) unsigned char smem_raw[];
+  const int D = g.row(), R = g.kv_rank, LDQ = lat_ldq(D);
+  bf* Qs = reinterpret_cast<bf*>(smem_raw);                       // [16][LDQ]
+  bf* Ks = Qs + (size_t)LATENT_PAIRS * LDQ;                       // [2][32][LDQ]
+  float* Sp = reinterpret_cast<float*>(Ks + (size_t)2 * KV_BLOCK * LDQ);  // [2][16][33]
+  bf* Ps = reinterpret_cast<bf*>(Sp + 2 * LATENT_PAIRS * 33);     // [16][40]
+  float* corr_s = reinterpret_cast<float*>(Ps + LATENT_PAIRS * 40);  // [16]
+  float* l_s = corr_s + LATENT_PAIRS;                             // [16]
+  griddep_launch();
+  griddep_wait();
+  const LatentTile tile = tiles[blockIdx.x];
+  const AttnSeq sq = seqs[tile.seq];
+  const int h0 = blockIdx.y * LATENT_PAIRS;
+  const int nh = min(g.heads - h0, LATENT_PAIRS);
+  const int npairs = tile.nq * nh;
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int pos0 = sq.kv_len - sq.q_len + tile.q0;
+  const int row0 = sq.q_start + tile.q0;
+  // zero everything once (unused pair rows, the k padding of Q and of both K buffers), then fill Q
+  {
+    uint32_t* z = reinterpret_cast<uint32_t*>(smem_raw);
+    const int n_words = (LATENT_PAIRS + 2 * KV_BLOCK) * LDQ / 2;
+    for (int i = tid; i < n_words; i += LAT_THREADS) z[i] = 0u;
+  }
+  __syncthreads();
+  for (int e = tid; e < npairs * D; e += LAT_THREADS) {
+    const int p = e / D, d = e - p * D;
+    const int tq = p / nh, h = h0 + p - tq * nh;
+    Qs[(size_t)p * LDQ + d] = __float2bfloat16_rn(q_abs[((size_t)(row0 + tq) * g.heads + h) * D + d] * g.scale);
+  }
+  const int pos_last = pos0 + tile.nq - 1;
+  const int kmin = g.window > 0 ? max(0, pos0 - g.window + 1) : 0;
+  const int blk0 = kmin / KV_BLOCK, blk1 = pos_last / KV_BLOCK;
+  const int32_t* bt = block_table + (size_t)sq.block_row * bt_stride;
+  const int chunks_per_row = D / 8;
+  auto load_block = [&](int blk, int st) {
+    const bf* src = cache + (size_t)bt[blk] * KV_BLOCK * D;
+    bf* dst = Ks + (size_t)st * KV_BLOCK * LDQ;
+    for (int c = tid; c < KV_BLOCK * chunks_per_row; c += LAT_THREADS) {
+      const int r = c / chunks_per_row, cc = c - r * chunks_per_row;
+      lat_cp_async_16(dst + (size_t)r * LDQ + cc * 8, src + (size_t)r * D + cc * 8);
+    }
+    asm volatile("cp.async.commit_group;\n" ::: "memory");
+  };
+  // softmax rows of this warp (two pairs), as in the FMA kernel
+  int prow[2], posq[2];
+  bool on[2];
+#pragma unroll
+  for (int u = 0; u < 2; ++u) {
+    prow[u] = warp + u * LAT_WARPS;
+    on[u] = prow[u] < npairs;
+    posq[u] = on[u] ? pos0 + prow[u] / nh : -1;
+  }
+  float m_run[2] = {-FLT_MAX, -FLT_MAX}, l_run[2] = {0.f, 0.f};
+  float acc[NT][4];
+#pragma unroll
+  for (int j = 0; j < NT; ++j)
+#pragma unroll
+    for (int e = 0; e < 4; ++e) acc[j][e] = 0.f;
+  const int KS = (D + 15) / 16, half = warp >> 2, ntk = warp & 3;
+  const int ks_lo = half == 0 ? 0 : KS / 2, ks_hi = half == 0 ? KS / 2 : KS;
+  const int gq = lane >> 2, t2 = (lane & 3) * 2;
+
+  load_block(blk0, 0);
+  for (int blk = blk0; blk <= blk1; ++blk) {
+    const int st = (blk - blk0) & 1;
+    asm volatile("cp.async.wait_group 0;\n" ::: "memory");
+    __syncthreads();  // block `blk` has landed for everyone; everyone is done with the other buffer, P, S and corr
+    if (blk < blk1) load_block(blk + 1, st ^ 1);
+    const bf* Kb = Ks + (size_t)st * KV_BLOCK * LDQ;
+    {  // ---- scores: this warp's 8 keys over its half of the row length
+      float c[4] = {0.f, 0.f, 0.f, 0.f};
+      for (int ks = ks_lo; ks < ks_hi; ++ks) {
+        uint32_t a[4], b[2];
+        lat_ldsm_x4(a, Qs + (size_t)(lane & 15) * LDQ + ks * 16 + (lane >> 4) * 8);
+        lat_ldsm_x2(b, Kb + (size_t)(ntk * 8 + (lane & 7)) * LDQ + ks * 16 + ((lane >> 3) & 1) * 8);
+        lat_mma(c, a, b[0], b[1]);
+      }
+      float* sp = Sp + (size_t)half * LATENT_PAIRS * 33;
+      sp[gq * 33 + ntk * 8 + t2] = c[0];
+      sp[gq * 33 + ntk * 8 + t2 + 1] = c[1];
+      sp[(gq + 8) * 33 + ntk * 8 + t2] = c[2];
+      sp[(gq + 8) * 33 + ntk * 8 + t2 + 1] = c[3];
+    }
+    __syncthreads();
+    {  // ---- softmax: rows warp and warp + 8, lane = key
+      const int kp = blk * KV_BLOCK + lane;
+#pragma unroll
+      for (int u = 0; u < 2; ++u) {
+        const int r = prow[u];
+        const bool vis = on[u] && kp <= posq[u] && (g.window <= 0 || posq[u] - kp < g.window);
+        const float sv = vis ? Sp[r * 33 + lane] + Sp[(LATENT_PAIRS + r) * 33 + lane] : -FLT_MAX;
+        const float m_new = fmaxf(m_run[u], warp_max_f(sv));
+        const float corr = m_new == -FLT_MAX ? 1.f : expf(m_run[u] - m_new);
+        const float p = vis ? expf(sv - m_new) : 0.f;
+        l_run[u] = l_run[u] * corr + warp_sum_f(p);
+        m_run[u] = m_new;
+        Ps[r * 40 + lane] = __float2bfloat16_rn(p);
+        if (lane == 0) corr_s[r] = corr;
+      }
+    }
+    __syncthreads();
+    {  // ---- output: rescale, then O += P C over this warp's column tiles
+      const float c_lo = corr_s[gq], c_hi = corr_s[gq + 8];
+      uint32_t a0[4], a1[4];
+      lat_ldsm_x4(a0, Ps + (size_t)(lane & 15) * 40 + (lane >> 4) * 8);
+      lat_ldsm_x4(a1, Ps + (size_t)(lane & 15) * 40 + 16 + (lane >> 4) * 8);
+#pragma unroll
+      for (int j = 0; j < NT; ++j) {
+        const int n0 = (warp + LAT_WARPS * j) * 8;
+        if (n0 < R) {
+          acc[j][0] *= c_lo; acc[j][1] *= c_lo; acc[j][2] *= c_hi; acc[j][3] *= c_hi;
+          uint32_t b[4];
+          lat_ldsm_x4_trans(b, Kb + (size_t)lane * LDQ + n0);
+          lat_mma(acc[j], a0, b[0], b[1]);
+          lat_mma(acc[j], a1, b[2], b[3]);
+        }
+      }
+    }
+  }
+  if (lane == 0) {
+    if (on[0]) l_s[prow[0]] = l_run[0];
+    if (on[1]) l_s[prow[1]] = l_run[1];
+  }
+  __syncthreads();
+#pragma unroll
+  for (int hf = 0; hf < 2; ++hf) {
+    const int p = gq + hf * 8;
+    if (p >= npairs) continue;
+    const int tq = p / nh, h = h0 + p - tq * nh;
+    const size_t o = ((size_t)(row0 + tq) * g.heads + h) * R;
+    const float inv = 1.f / l_s[p];
+#pragma unroll
+    for (int j = 0; j < NT; ++j) {
+      const int n = (warp + LAT_WARPS * j) * 8 + t2;
+      if (n < R) {
+        st_any(o_lat, o_dtype, o + n, acc[j][hf * 2] * inv);
+        st_any(o_lat, o_dtype, o + n + 1, acc[j][hf * 2 + 1] * inv);
+      }
+    }
+  }
+}
+
+template <int NT>
+cudaError_t launch_attn_mma(const float* q_abs, const void* cache, const AttnSeq* seqs, const LatentTile* tiles, int n_tiles,
+                            const int32_t* block_table, int bt_stride, void* o_lat, int o_dtype, const LatentGeom& g,
+                            cudaStream_t stream) {
+  const size_t smem = lat_mma_smem(g.row());
+  static size_t attr_bytes = 0;
+  if (smem > 48 * 1024 && smem > attr_bytes) {
+    const cudaError_t e = cudaFuncSetAttribute(latent_attn_mma_kernel<NT>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (e != cudaSuccess) return e;
+    attr_bytes = smem;
+  }
+  const dim3 grid(n_tiles, (g.heads + LATENT_PAIRS - 1) / LATENT_PAIRS);
+  return launch_k(latent_attn_mma_kernel<NT>, grid, dim3(LAT_THREADS), smem, stream, q_abs,
+                  reinterpret_cast<const __nv_bfloat16*>(cache), seqs, tiles, block_table, bt_stride, o_lat, o_dtype, g);
+}
+
+bool latent_mma_eligible(const void* cache, int dtype, const LatentGeom& g) {
+  static int on = -1;
+  if (on < 0) {
+    const char* e = getenv("TGIS_LATENT_ATTN_MMA");
+    on = (e && e[0] == '0') ? 0 : 1;
+  }
+  return on && dtype == DT_BF16 && g.row() % 8 == 0 && g.kv_rank % 8 == 0 && g.kv_rank <= 512 &&
+         (reinterpret_cast<uintptr_t>(cache) & 15) == 0 && lat_mma_smem(g.row()) <= 200 * 1024;
+}
+
 template <class CT, int NACC>
 cudaError_t launch_attn(const float* q_abs, const void* cache, const AttnSeq* seqs, const LatentTile* tiles, int n_tiles,
                         const int32_t* block_table, int bt_stride, void* o_lat, int o_dtype, const LatentGeom& g,
@@ -272,6 +489,11 @@ cudaError_t latent_attn_launch(const float* q_abs, const void* cache, int dtype,
                                const LatentTile* tiles, int n_tiles, const int32_t* block_table, int bt_stride,
                                void* o_lat, int o_dtype, const LatentGeom& g, cudaStream_t stream) {
   if (n_tiles <= 0) return cudaSuccess;
+  if (latent_mma_eligible(cache, dtype, g)) {
+    if (g.kv_rank <= 128) return launch_attn_mma<2>(q_abs, cache, seqs, tiles, n_tiles, block_table, bt_stride, o_lat, o_dtype, g, stream);
+    if (g.kv_rank <= 256) return launch_attn_mma<4>(q_abs, cache, seqs, tiles, n_tiles, block_table, bt_stride, o_lat, o_dtype, g, stream);
+    return launch_attn_mma<8>(q_abs, cache, seqs, tiles, n_tiles, block_table, bt_stride, o_lat, o_dtype, g, stream);
+  }
   if (dtype == DT_BF16)
     return launch_attn_ct<__nv_bfloat16>(q_abs, cache, seqs, tiles, n_tiles, block_table, bt_stride, o_lat, o_dtype, g, stream);
   return launch_attn_ct<float>(q_abs, cache, seqs, tiles, n_tiles, block_table, bt_stride, o_lat, o_dtype, g, stream);

@@ -49,6 +49,10 @@ PRESETS: dict[str, ModelConfig] = {
                             max_model_len=512, arch="opt"),
     "llama3-8b": ModelConfig(n_layers=32, hidden=4096, n_q_heads=32, n_kv_heads=8, ffn=14336, vocab=128256,
                              max_model_len=8192),
+    # --- arch-compare sizes (bench.py --arch-compare): Llama stacks with the hidden size, layer count and ACTIVE feed-forward
+    # width per token of the Ponenex sizes in engine/ponenex.py PRESETS
+    "llama-cmp-1k": ModelConfig(n_layers=4, hidden=1024, n_q_heads=8, n_kv_heads=2, ffn=3072, vocab=32768, max_model_len=4096),
+    "llama-cmp-2k": ModelConfig(n_layers=4, hidden=2048, n_q_heads=16, n_kv_heads=4, ffn=11264, vocab=32768, max_model_len=4096),
     "llama3-70b": ModelConfig(n_layers=80, hidden=8192, n_q_heads=64, n_kv_heads=8, ffn=28672, vocab=128256,
                               max_model_len=8192),
 }

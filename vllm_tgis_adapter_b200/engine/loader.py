@@ -92,9 +92,10 @@ def load_synthetic_weights(eng: NativeEngine, mc: ModelConfig, seed: int, device
         return (torch.randn(r, c, generator=gen, device=f"cuda:{device}", dtype=torch.float32) * 0.02).to(torch.bfloat16)
 
     if mc.arch == "ponenex":
-        from .ponenex import synthetic_weights
+        from .ponenex import iter_synthetic_weights
 
-        eng.load_weights(synthetic_weights(mc, seed, f"cuda:{device}"))
+        for name, t in iter_synthetic_weights(mc, seed, f"cuda:{device}"):
+            eng.load_weight(name, t)
         return
 
     if mc.arch == "opt":
@@ -174,10 +175,14 @@ def _resolve_model(args):
         if dtype == "float32" and mc.arch != "ponenex":
             raise ValueError(f"--dtype float32 is not available for the {mc.arch} architecture (bfloat16 only)")
         return mc, path
-    if args.model in PRESETS:
+    from .ponenex import PRESETS as PONENEX_PRESETS
+
+    if args.model in PRESETS or args.model in PONENEX_PRESETS:
         if not args.synthetic_weights:
             raise ValueError(f"--model {args.model} is a preset name: pass --synthetic-weights or a model directory")
-        mc = dataclasses.replace(PRESETS[args.model])
+        mc = dataclasses.replace((PRESETS.get(args.model) or PONENEX_PRESETS[args.model]))
+        if mc.arch == "ponenex" and getattr(args, "dtype", "auto") in ("float32", "fp32"):
+            mc.dtype = "float32"
         if args.max_model_len:
             mc.max_model_len = args.max_model_len
         return mc, None

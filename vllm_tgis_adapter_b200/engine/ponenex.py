@@ -114,18 +114,39 @@ def tensor_shapes(mc: ModelConfig) -> dict[str, tuple[int, ...]]:
     return out
 
 
-def synthetic_weights(mc: ModelConfig, seed: int, device: str = "cpu") -> dict:
-    """Seeded random bf16 weights of the architecture (norm weights around zero, matrices ~ N(0, 1 / fan_in))."""
+def iter_synthetic_weights(mc: ModelConfig, seed: int, device: str = "cpu"):
+    """Seeded random bf16 weights of the architecture, one (name, tensor) at a time, drawn on `device` (norm weights around
+    zero, the latents' plain norm weights around one, matrices ~ N(0, 1 / fan_in))."""
     import torch
 
-    gen = torch.Generator(device="cpu").manual_seed(seed)
-    out = {}
+    gen = torch.Generator(device=device).manual_seed(seed)
     for name, shape in tensor_shapes(mc).items():
         if len(shape) == 1:
-            t = torch.randn(shape, generator=gen) * (0.5 if name.endswith("router.b") else 0.1)
+            t = torch.randn(shape, generator=gen, device=device) * (0.5 if name.endswith("router.b") else 0.1)
             if name.endswith(".norm") and name != "final.norm":
-                t = t + 1.0   # the latents' norms carry plain weights
+                t = t + 1.0
         else:
-            t = torch.randn(shape, generator=gen) * (1.0 if name == "embed" else shape[1] ** -0.5)
-        out[name] = t.to(torch.bfloat16).to(device)
-    return out
+            t = torch.randn(shape, generator=gen, device=device) * (1.0 if name == "embed" else shape[1] ** -0.5)
+        yield name, t.to(torch.bfloat16)
+
+
+def synthetic_weights(mc: ModelConfig, seed: int, device: str = "cpu") -> dict:
+    return dict(iter_synthetic_weights(mc, seed, device))
+
+
+def _uniform(n_layers: int, hidden: int, vocab: int, **layer) -> ModelConfig:
+    return ModelConfig(n_layers=n_layers, hidden=hidden, n_q_heads=1, n_kv_heads=1, ffn=64, vocab=vocab, rms_eps=1e-5,
+                       max_model_len=4096, arch="ponenex", layers=[LayerSpec(**layer) for _ in range(n_layers)],
+                       embed_scale=1.0, residual_mult=1.0)
+
+
+# Sizes that resemble the layers of real latent-attention / mixture-of-experts models (random weights; `--model <name>
+# --synthetic-weights`, bench.py --arch-compare)
+PRESETS: dict[str, ModelConfig] = {
+    "ponenex-tiny": _uniform(2, 256, 1024, heads=4, dim=32, rot_dim=16, vdim=32, kv_rank=64, q_rank=128, window=128,
+                             rot_dims=16, rot_base=10000.0, scale=48 ** -0.5, experts=8, top=2, expert_ff=128, shared_ff=128),
+    "ponenex-1k": _uniform(4, 1024, 32768, heads=8, dim=128, rot_dim=64, vdim=128, kv_rank=256, q_rank=768, window=2048,
+                           rot_dims=64, rot_base=10000.0, scale=192 ** -0.5, experts=16, top=2, expert_ff=1024, shared_ff=1024),
+    "ponenex-2k": _uniform(4, 2048, 32768, heads=16, dim=128, rot_dim=64, vdim=128, kv_rank=512, q_rank=1536, window=4096,
+                           rot_dims=64, rot_base=10000.0, scale=192 ** -0.5, experts=64, top=6, expert_ff=1408, shared_ff=2816),
+}
