@@ -7,6 +7,7 @@
 // All of them are 16-byte vectorised, coalesced, one row (or 8 elements) per thread group; no shared-memory reuse is
 // possible (each byte is touched once) so the design target is simply full-width coalesced traffic.
 #include <algorithm>
+#include <cstdint>
 
 #include "kernels.h"
 #include "launch.cuh"
@@ -675,44 +676,98 @@ cudaError_t embed_scale_f32_launch(const int32_t* token_ids, const void* table, 
                   vocab);
 }
 
+// VEC = 4: hidden % 4 == 0, every row read and written as 16-byte (fp32) / 8-byte (bf16) vectors; VEC = 1: any width
+template <int VEC>
+struct FV { float v[VEC]; };
+template <int VEC>
+__device__ __forceinline__ FV<VEC> ld_fv(const float* p) {
+  FV<VEC> r;
+  if (VEC == 4) {
+    const float4 q = *reinterpret_cast<const float4*>(p);
+    r.v[0] = q.x; r.v[1 % VEC] = q.y; r.v[2 % VEC] = q.z; r.v[3 % VEC] = q.w;
+  } else {
+    r.v[0] = *p;
+  }
+  return r;
+}
+template <int VEC>
+__device__ __forceinline__ void st_fv(float* p, const FV<VEC>& r) {
+  if (VEC == 4) *reinterpret_cast<float4*>(p) = make_float4(r.v[0], r.v[1 % VEC], r.v[2 % VEC], r.v[3 % VEC]);
+  else *p = r.v[0];
+}
+
+template <int VEC>
 __global__ void __launch_bounds__(NORM_THREADS) resid_tail_kernel(ResidTail a, int hidden) {
-  extern __shared__ float row_buf[];
+  extern __shared__ __align__(16) float row_buf[];
   __shared__ float red[NORM_THREADS / 32];
   griddep_launch();
   griddep_wait();
   const int t = blockIdx.x;
   const size_t base = (size_t)t * hidden;
   float ss = 0.f;
-  for (int i = threadIdx.x; i < hidden; i += NORM_THREADS) {
-    float y = 0.f;
+  for (int i = threadIdx.x * VEC; i < hidden; i += NORM_THREADS * VEC) {
+    FV<VEC> y;
+#pragma unroll
+    for (int e = 0; e < VEC; ++e) y.v[e] = 0.f;
     if (a.y_main != nullptr) {
-      y = a.y_main[base + i];
+      y = ld_fv<VEC>(a.y_main + base + i);
     } else {
       if (a.y_rows != nullptr)
-        for (int k = 0; k < a.top; ++k)
-          y = fmaf(a.mix_w[(size_t)t * a.top + k], a.y_rows[(size_t)a.inv[(size_t)t * a.top + k] * hidden + i], y);
-      if (a.y_side != nullptr) y = fmaf(a.side_gate != nullptr ? a.side_gate[t] : 1.f, a.y_side[base + i], y);
+        for (int k = 0; k < a.top; ++k) {
+          const float w = a.mix_w[(size_t)t * a.top + k];
+          const FV<VEC> r = ld_fv<VEC>(a.y_rows + (size_t)a.inv[(size_t)t * a.top + k] * hidden + i);
+#pragma unroll
+          for (int e = 0; e < VEC; ++e) y.v[e] = fmaf(w, r.v[e], y.v[e]);
+        }
+      if (a.y_side != nullptr) {
+        const float w = a.side_gate != nullptr ? a.side_gate[t] : 1.f;
+        const FV<VEC> r = ld_fv<VEC>(a.y_side + base + i);
+#pragma unroll
+        for (int e = 0; e < VEC; ++e) y.v[e] = fmaf(w, r.v[e], y.v[e]);
+      }
     }
-    row_buf[i] = y;
-    ss += y * y;
+    st_fv<VEC>(row_buf + i, y);
+#pragma unroll
+    for (int e = 0; e < VEC; ++e) ss += y.v[e] * y.v[e];
   }
   const float rs = 1.f / sqrtf(block_sum<NORM_THREADS>(ss, red) / (float)hidden + a.eps);
   float ss2 = 0.f;
-  for (int i = threadIdx.x; i < hidden; i += NORM_THREADS) {
-    const float r = a.resid[base + i] + a.mult * (row_buf[i] * rs * (a.w_off + a.w_post[i]));
-    a.resid[base + i] = r;
-    row_buf[i] = r;
-    ss2 += r * r;
+  for (int i = threadIdx.x * VEC; i < hidden; i += NORM_THREADS * VEC) {
+    const FV<VEC> y = ld_fv<VEC>(row_buf + i), x = ld_fv<VEC>(a.resid + base + i), w = ld_fv<VEC>(a.w_post + i);
+    FV<VEC> r;
+#pragma unroll
+    for (int e = 0; e < VEC; ++e) {
+      r.v[e] = x.v[e] + a.mult * (y.v[e] * rs * (a.w_off + w.v[e]));
+      ss2 += r.v[e] * r.v[e];
+    }
+    st_fv<VEC>(a.resid + base + i, r);
+    st_fv<VEC>(row_buf + i, r);
   }
   if (a.w_pre == nullptr) return;
   const float rs2 = 1.f / sqrtf(block_sum<NORM_THREADS>(ss2, red) / (float)hidden + a.eps);
-  for (int i = threadIdx.x; i < hidden; i += NORM_THREADS)
-    st_dt(a.out, a.out_dtype, base + i, row_buf[i] * rs2 * (a.w_off + a.w_pre[i]));
+  for (int i = threadIdx.x * VEC; i < hidden; i += NORM_THREADS * VEC) {
+    const FV<VEC> r = ld_fv<VEC>(row_buf + i), w = ld_fv<VEC>(a.w_pre + i);
+    if (VEC == 4 && a.out_dtype == DT_BF16) {
+      __nv_bfloat162 lo = __floats2bfloat162_rn(r.v[0] * rs2 * (a.w_off + w.v[0]), r.v[1 % VEC] * rs2 * (a.w_off + w.v[1 % VEC]));
+      __nv_bfloat162 hi = __floats2bfloat162_rn(r.v[2 % VEC] * rs2 * (a.w_off + w.v[2 % VEC]), r.v[3 % VEC] * rs2 * (a.w_off + w.v[3 % VEC]));
+      uint2 pk;
+      pk.x = *reinterpret_cast<uint32_t*>(&lo);
+      pk.y = *reinterpret_cast<uint32_t*>(&hi);
+      *reinterpret_cast<uint2*>(reinterpret_cast<__nv_bfloat16*>(a.out) + base + i) = pk;
+    } else {
+#pragma unroll
+      for (int e = 0; e < VEC; ++e) st_dt(a.out, a.out_dtype, base + i + e, r.v[e] * rs2 * (a.w_off + w.v[e]));
+    }
+  }
 }
 cudaError_t resid_tail_launch(const ResidTail& a, int T, int hidden, cudaStream_t stream) {
   if (T <= 0) return cudaSuccess;
   if (a.w_post == nullptr || a.resid == nullptr || (size_t)hidden * 4 > 48 * 1024) return cudaErrorInvalidValue;
-  return launch_k(resid_tail_kernel, dim3(T), dim3(NORM_THREADS), (size_t)hidden * sizeof(float), stream, a, hidden);
+  auto al16 = [](const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; };
+  const bool vec = hidden % 4 == 0 && al16(a.y_main) && al16(a.y_rows) && al16(a.y_side) && al16(a.resid) && al16(a.w_post) &&
+                   al16(a.w_pre) && al16(a.out);
+  if (vec) return launch_k(resid_tail_kernel<4>, dim3(T), dim3(NORM_THREADS), (size_t)hidden * sizeof(float), stream, a, hidden);
+  return launch_k(resid_tail_kernel<1>, dim3(T), dim3(NORM_THREADS), (size_t)hidden * sizeof(float), stream, a, hidden);
 }
 
 __global__ void gather_rows_any_kernel(const int32_t* __restrict__ idx, const uint8_t* __restrict__ x,

@@ -140,11 +140,11 @@ __global__ void __launch_bounds__(ANY_THREADS) gemm_any_kernel(GemmAny a) {
 }
 
 // ---- tensor-core variant (bf16 operands, 16-byte aligned rows): mma.sync m16n8k16, fp32 accumulators ---------------
-// CTA tile 64 rows x 128 weight rows, k-blocks of 32 double-buffered with cp.async (out-of-range rows and the k tail are
-// zero-filled by the copy), 8 warps as 2 x 4, warp tile 32 x 32; operands reach the registers through ldmatrix from rows
+// CTA tile 64 or 128 rows x 128 weight rows, k-blocks of 32 in a three-stage cp.async ring (out-of-range rows and the k tail
+// are zero-filled by the copy), 8 warps as 2 x 4; operands reach the registers through ldmatrix from rows
 // padded to 80 bytes (conflict-free).  Same geometries and epilogues as the FMA kernel; the k order inside an output
 // element is fixed (ascending k-blocks, the MMA's own order inside), so a row's result does not depend on its neighbours.
-constexpr int MMA_BM = 64, MMA_BN = 128, MMA_BK = 32, MMA_LD = MMA_BK + 8;
+constexpr int MMA_BN = 128, MMA_BK = 32, MMA_LD = MMA_BK + 8;
 
 __device__ __forceinline__ void cp_async_16(void* smem, const void* gmem, bool valid) {
   const uint32_t s = (uint32_t)__cvta_generic_to_shared(smem);
@@ -165,12 +165,20 @@ __device__ __forceinline__ void mma_bf16_16816(float (&c)[4], const uint32_t (&a
                : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
 }
 
-template <class OT>
+// MI = 16-row MMA tiles per warp along M: CTA tile (32 MI) rows x 128 weight rows (MI = 2: 64 rows, MI = 4: 128 rows).
+// Dynamic shared memory: MMA_STAGES x (32 MI + 128) rows of MMA_LD bf16.
+constexpr int MMA_STAGES = 3;
+template <int MI>
+constexpr size_t mma_smem_bytes() { return (size_t)MMA_STAGES * (32 * MI + MMA_BN) * MMA_LD * 2; }
+
+template <class OT, int MI>
 __global__ void __launch_bounds__(ANY_THREADS) gemm_any_mma_kernel(GemmAny a) {
   using bf = __nv_bfloat16;
-  __shared__ __align__(16) bf Xs[2][MMA_BM][MMA_LD];
-  __shared__ __align__(16) bf Ws[2][MMA_BN][MMA_LD];
-  __shared__ int row_src[MMA_BM], row_dst[MMA_BM];
+  constexpr int BM = 32 * MI;
+  extern __shared__ __align__(16) unsigned char mma_smem[];
+  bf* Xs = reinterpret_cast<bf*>(mma_smem);                 // [stage][BM][MMA_LD]
+  bf* Ws = Xs + (size_t)MMA_STAGES * BM * MMA_LD;           // [stage][MMA_BN][MMA_LD]
+  __shared__ int row_src[BM], row_dst[BM];
   griddep_launch();
   griddep_wait();
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
@@ -179,18 +187,18 @@ __global__ void __launch_bounds__(ANY_THREADS) gemm_any_mma_kernel(GemmAny a) {
     int t = blockIdx.y;
     for (; group < a.n_groups; ++group) {
       const int cnt = a.seg_off[group + 1] - a.seg_off[group];
-      const int nt = (cnt + MMA_BM - 1) / MMA_BM;
+      const int nt = (cnt + BM - 1) / BM;
       if (t < nt) break;
       t -= nt;
     }
     if (group >= a.n_groups) return;
-    row0 = a.seg_off[group] + t * MMA_BM;
+    row0 = a.seg_off[group] + t * BM;
     row_end = a.seg_off[group + 1];
   } else {
-    row0 = blockIdx.y * MMA_BM;
+    row0 = blockIdx.y * BM;
     row_end = a.T;
   }
-  if (tid < MMA_BM) {
+  if (tid < BM) {
     const int r = row0 + tid;
     row_src[tid] = r < row_end ? (a.gather != nullptr ? a.gather[r] / a.gather_div : r) : -1;
     row_dst[tid] = r < row_end ? r : -1;
@@ -201,66 +209,71 @@ __global__ void __launch_bounds__(ANY_THREADS) gemm_any_mma_kernel(GemmAny a) {
   const bf* W = reinterpret_cast<const bf*>(a.W) + (size_t)z * a.w_bs + (size_t)group * a.w_gs;
   OT* Y = reinterpret_cast<OT*>(a.Y) + (size_t)z * a.y_bs;
   const int n0 = blockIdx.x * MMA_BN;
-  const int wm = warp >> 2, wn = warp & 3;  // 2 x 4 warps
+  const int wm = warp >> 2, wn = warp & 3;  // 2 x 4 warps, warp tile (16 MI) x 32
 
   auto stage_load = [&](int st, int k0) {
-    {  // X: 64 rows x 4 chunks of 8 elements
-      const int r = tid >> 2, c = tid & 3;
+    bf* xs = Xs + (size_t)st * BM * MMA_LD;
+    bf* ws = Ws + (size_t)st * MMA_BN * MMA_LD;
+#pragma unroll
+    for (int i = 0; i < BM / 64; ++i) {  // X: BM rows x 4 chunks of 8 elements
+      const int id = tid + i * ANY_THREADS;
+      const int r = id >> 2, c = id & 3;
       const int src = row_src[r];
       const bool ok = src >= 0 && k0 + c * 8 < a.K;
-      cp_async_16(&Xs[st][r][c * 8], ok ? X + (size_t)src * a.ldx + k0 + c * 8 : X, ok);
+      cp_async_16(xs + (size_t)r * MMA_LD + c * 8, ok ? X + (size_t)src * a.ldx + k0 + c * 8 : X, ok);
     }
 #pragma unroll
     for (int i = 0; i < 2; ++i) {  // W: 128 rows x 4 chunks
       const int id = tid + i * ANY_THREADS;
       const int n = id >> 2, c = id & 3;
       const bool ok = n0 + n < a.N && k0 + c * 8 < a.K;
-      cp_async_16(&Ws[st][n][c * 8], ok ? W + (size_t)(n0 + n) * a.ldw + k0 + c * 8 : W, ok);
+      cp_async_16(ws + (size_t)n * MMA_LD + c * 8, ok ? W + (size_t)(n0 + n) * a.ldw + k0 + c * 8 : W, ok);
     }
-    cp_async_commit();
   };
 
-  float acc[2][4][4];
+  float acc[MI][4][4];
 #pragma unroll
-  for (int i = 0; i < 2; ++i)
+  for (int i = 0; i < MI; ++i)
 #pragma unroll
     for (int j = 0; j < 4; ++j)
 #pragma unroll
       for (int e = 0; e < 4; ++e) acc[i][j][e] = 0.f;
 
   const int KB = (a.K + MMA_BK - 1) / MMA_BK;
-  stage_load(0, 0);
+#pragma unroll
+  for (int s = 0; s < MMA_STAGES - 1; ++s) {  // prologue (one commit group per stage, empty ones included)
+    if (s < KB) stage_load(s, s * MMA_BK);
+    cp_async_commit();
+  }
   for (int kb = 0; kb < KB; ++kb) {
-    const int st = kb & 1;
-    if (kb + 1 < KB) {
-      stage_load(st ^ 1, (kb + 1) * MMA_BK);
-      cp_async_wait<1>();
-    } else {
-      cp_async_wait<0>();
-    }
-    __syncthreads();
+    cp_async_wait<MMA_STAGES - 2>();  // k-block kb has landed (for this thread's copies)
+    __syncthreads();                  // ... for everyone's; and everyone is done with the stage refilled below
+    if (kb + MMA_STAGES - 1 < KB) stage_load((kb + MMA_STAGES - 1) % MMA_STAGES, (kb + MMA_STAGES - 1) * MMA_BK);
+    cp_async_commit();
+    const bf* xs = Xs + (size_t)(kb % MMA_STAGES) * BM * MMA_LD;
+    const bf* ws = Ws + (size_t)(kb % MMA_STAGES) * MMA_BN * MMA_LD;
 #pragma unroll
     for (int ks = 0; ks < MMA_BK / 16; ++ks) {
-      uint32_t af[2][4], bfr[2][4];
+      uint32_t af[MI][4], bfr[2][4];
 #pragma unroll
-      for (int mi = 0; mi < 2; ++mi) ldsm_x4(af[mi], &Xs[st][wm * 32 + mi * 16 + (lane & 15)][ks * 16 + (lane >> 4) * 8]);
+      for (int mi = 0; mi < MI; ++mi)
+        ldsm_x4(af[mi], xs + (size_t)(wm * 16 * MI + mi * 16 + (lane & 15)) * MMA_LD + ks * 16 + (lane >> 4) * 8);
 #pragma unroll
       for (int nj = 0; nj < 2; ++nj)
-        ldsm_x4(bfr[nj], &Ws[st][wn * 32 + nj * 16 + (lane >> 4) * 8 + (lane & 7)][ks * 16 + ((lane >> 3) & 1) * 8]);
+        ldsm_x4(bfr[nj], ws + (size_t)(wn * 32 + nj * 16 + (lane >> 4) * 8 + (lane & 7)) * MMA_LD + ks * 16 + ((lane >> 3) & 1) * 8);
 #pragma unroll
-      for (int mi = 0; mi < 2; ++mi)
+      for (int mi = 0; mi < MI; ++mi)
 #pragma unroll
         for (int ni = 0; ni < 4; ++ni) mma_bf16_16816(acc[mi][ni], af[mi], bfr[ni >> 1][(ni & 1) * 2], bfr[ni >> 1][(ni & 1) * 2 + 1]);
     }
-    __syncthreads();
   }
   // ---- epilogue: a thread holds columns (2t, 2t + 1) of rows g and g + 8 of every 16 x 8 block
   const int g = lane >> 2, t2 = (lane & 3) * 2;
 #pragma unroll
-  for (int mi = 0; mi < 2; ++mi)
+  for (int mi = 0; mi < MI; ++mi)
 #pragma unroll
     for (int half = 0; half < 2; ++half) {
-      const int dst = row_dst[wm * 32 + mi * 16 + g + half * 8];
+      const int dst = row_dst[wm * 16 * MI + mi * 16 + g + half * 8];
       if (dst < 0) continue;
       const float s = a.mode == GEMM_ANY_ROWSCALE ? a.row_scale[(size_t)dst * a.scale_ld + z] : 1.f;
 #pragma unroll
@@ -277,12 +290,27 @@ __global__ void __launch_bounds__(ANY_THREADS) gemm_any_mma_kernel(GemmAny a) {
     }
 }
 
-template <class OT>
-cudaError_t launch_mma(const GemmAny& a, cudaStream_t stream) {
-  const int row_tiles = a.seg_off != nullptr ? (a.T + MMA_BM - 1) / MMA_BM + a.n_groups : (a.T + MMA_BM - 1) / MMA_BM;
+template <class OT, int MI>
+cudaError_t launch_mma_mi(const GemmAny& a, cudaStream_t stream) {
+  constexpr int BM = 32 * MI;
+  static bool attr_set = false;
+  if (!attr_set) {
+    const cudaError_t e = cudaFuncSetAttribute(gemm_any_mma_kernel<OT, MI>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                               (int)mma_smem_bytes<MI>());
+    if (e != cudaSuccess) return e;
+    attr_set = true;
+  }
+  const int row_tiles = a.seg_off != nullptr ? (a.T + BM - 1) / BM + a.n_groups : (a.T + BM - 1) / BM;
   const dim3 grid((a.N + MMA_BN - 1) / MMA_BN, row_tiles, a.batch > 0 ? a.batch : 1);
   if (grid.y > 65535 || grid.z > 65535) return cudaErrorInvalidValue;
-  return launch_k(gemm_any_mma_kernel<OT>, grid, dim3(ANY_THREADS), 0, stream, a);
+  return launch_k(gemm_any_mma_kernel<OT, MI>, grid, dim3(ANY_THREADS), mma_smem_bytes<MI>(), stream, a);
+}
+
+template <class OT>
+cudaError_t launch_mma(const GemmAny& a, cudaStream_t stream) {
+  // 128-row tiles once the problems (or the average expert segment) are tall enough to fill them
+  const int rows = a.seg_off != nullptr ? (a.T + a.n_groups - 1) / (a.n_groups > 0 ? a.n_groups : 1) : a.T;
+  return rows > 96 ? launch_mma_mi<OT, 4>(a, stream) : launch_mma_mi<OT, 2>(a, stream);
 }
 
 bool mma_eligible(const GemmAny& a) {
