@@ -64,7 +64,7 @@ def _gemm_any(x, w, y, T, N, K, *, ldx=None, ldw=None, ldy=None, batch=1, x_bs=0
     torch.cuda.synchronize()
 
 
-@pytest.mark.parametrize("T,N,K", [(1, 6, 192), (5, 17, 33), (70, 130, 96), (200, 64, 100), (3, 448, 7)])
+@pytest.mark.parametrize("T,N,K", [(1, 5, 200), (5, 17, 33), (70, 130, 88), (200, 64, 100), (3, 440, 7)])
 @pytest.mark.parametrize("dt", [torch.float32, torch.bfloat16])
 def test_gemm_any_dense_any_shape(T, N, K, dt):
     g = torch.Generator().manual_seed(T * 1000 + N)
@@ -266,36 +266,43 @@ def test_latent_attention_prompt_portion_and_decode_match_dense_softmax(heads, k
 
 
 @pytest.mark.parametrize("q_len", [1, 5, 64])
-def test_latent_attention_one_key_decides_at_window_and_block_edges(q_len):
-    """Every key row carries its own position as a one-hot code in c and a strong match direction; the query is built so that
-    ONE chosen key outweighs all others by e^40.  If that key is visible the output is its code, otherwise it is not: a
-    window that is one token off, or a block that is skipped or read twice, flips the answer."""
-    heads, kv_rank, rot_dim, window, kv_len = 2, 200, 2, 72, 200
+@pytest.mark.parametrize("dt,window,kv_len", [(F32, 70, 200), (BF16, 70, 200), (BF16, 300, 500), (BF16, 0, 500)])
+def test_latent_attention_one_key_decides_at_window_and_block_edges(q_len, dt, window, kv_len):
+    """Every key row carries its own position as a one-hot code in c; the query is built so that ONE chosen key outweighs
+    all others by e^40.  If that key is visible the output is its code, otherwise the weight spreads evenly over what is
+    visible: a window that is one token off, or a block (or a split of blocks) that is skipped or read twice, flips the
+    answer.  bf16 rows run on the tensor cores; long key ranges of few queries are cut into splits and merged."""
+    heads, rot_dim = 2, 8
+    kv_rank = (kv_len + 7) // 8 * 8
     D = kv_rank + rot_dim
     rows = torch.zeros(kv_len, D)
     for j in range(kv_len):
         rows[j, j] = 1.0                                   # code of position j (kv_rank >= kv_len)
-    cache, blocks = _paged(rows, 8, q_len, torch.float32)
+    cache, blocks = _paged(rows, (kv_len + KV_BLOCK - 1) // KV_BLOCK + 3, q_len, _tdt(dt))
     geom = _geom(heads, 4, rot_dim, 4, kv_rank, 4, window, rot_dim, 1.0)
     bt = (C.c_int32 * len(blocks))(*blocks.tolist())
     last = kv_len - 1
     first_q = kv_len - q_len
-    # distances from the LAST query: itself, neighbours, block borders, the window's two sides, far away
-    for dist in [0, 1, last % KV_BLOCK, last % KV_BLOCK + 1, window - 2, window - 1, window, window + 1, 150, last]:
+    w_eff = window if window > 0 else 10 ** 9
+    # distances from the LAST query: itself, neighbours, block borders, split borders, the window's two sides, far away
+    dists = {0, 1, last % KV_BLOCK, last % KV_BLOCK + 1, last % 128, last % 128 + 1, 150, last}
+    if window > 0:
+        dists |= {window - 2, window - 1, window, window + 1}
+    for dist in sorted(d for d in dists if 0 <= d <= last):
         target = last - dist
         q_abs = torch.zeros(q_len, heads, D)
         q_abs[:, :, target] = 40.0
         o = torch.zeros(q_len, heads, kv_rank, device="cuda")
         seqs = (C.c_int32 * 4)(0, q_len, kv_len, 0)
-        _ok(_lib().tgis_k_latent_attn(_p(_dev(q_abs)), _p(cache), F32, seqs, 1, bt, 1, len(blocks), _p(o), F32, C.byref(geom)))
+        _ok(_lib().tgis_k_latent_attn(_p(_dev(q_abs)), _p(cache), dt, seqs, 1, bt, 1, len(blocks), _p(o), F32, C.byref(geom)))
         o = o.cpu()
         for t in range(q_len):
             pq = first_q + t
-            sees = 0 <= pq - target < window
+            sees = 0 <= pq - target < w_eff
             got = float(o[t, 1, target])
             assert (got > 0.99) == sees, (dist, t, got)
             if not sees:   # then the weight is spread evenly over what IS visible
-                n_vis = min(window, pq + 1)
+                n_vis = min(w_eff, pq + 1)
                 assert abs(float(o[t, 0, pq]) - 1.0 / n_vis) < 1e-5, (dist, t)
 
 

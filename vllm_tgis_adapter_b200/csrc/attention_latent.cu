@@ -10,6 +10,7 @@
 // the window are never touched), stages each 32-row block in shared memory once and lets every warp run two pairs
 // against it: lane = key for the scores, lane = latent dimension (strided by 32) for the weighted sum.  A query's
 // arithmetic depends only on its own position and on the block grid of its sequence, not on the tile or step it came in.
+#include <algorithm>
 #include <cfloat>
 #include <cstdint>
 #include <cstdlib>
@@ -264,7 +265,7 @@ __global__ void __launch_bounds__(LAT_THREADS)
 latent_attn_mma_kernel(const float* __restrict__ q_abs, const __nv_bfloat16* __restrict__ cache,
                        const AttnSeq* __restrict__ seqs, const LatentTile* __restrict__ tiles,
                        const int32_t* __restrict__ block_table, int bt_stride, void* __restrict__ o_lat, int o_dtype,
-                       LatentGeom g) {
+                       LatentGeom g, float* __restrict__ part, int n_splits) {
   using bf = __nv_bfloat16;
   extern __shared__ __align__(16) unsigned char smem_raw[];
   const int D = g.row(), R = g.kv_rank, LDQ = lat_ldq(D);
@@ -284,11 +285,12 @@ latent_attn_mma_kernel(const float* __restrict__ q_abs, const __nv_bfloat16* __r
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int pos0 = sq.kv_len - sq.q_len + tile.q0;
   const int row0 = sq.q_start + tile.q0;
-  // zero everything once (unused pair rows, the k padding of Q and of both K buffers), then fill Q
-  {
+  // zero once what no copy fills, then fill Q
+  {  // all of Q (unused pair rows, k padding); of the two K buffers only the columns behind D (the copies fill the rest)
     uint32_t* z = reinterpret_cast<uint32_t*>(smem_raw);
-    const int n_words = (LATENT_PAIRS + 2 * KV_BLOCK) * LDQ / 2;
-    for (int i = tid; i < n_words; i += LAT_THREADS) z[i] = 0u;
+    for (int i = tid; i < LATENT_PAIRS * LDQ / 2; i += LAT_THREADS) z[i] = 0u;
+    const int pad = LDQ - D;
+    for (int i = tid; i < 2 * KV_BLOCK * pad; i += LAT_THREADS) Ks[(size_t)(i / pad) * LDQ + D + i % pad] = __float2bfloat16_rn(0.f);
   }
   __syncthreads();
   for (int e = tid; e < npairs * D; e += LAT_THREADS) {
@@ -298,7 +300,24 @@ latent_attn_mma_kernel(const float* __restrict__ q_abs, const __nv_bfloat16* __r
   }
   const int pos_last = pos0 + tile.nq - 1;
   const int kmin = g.window > 0 ? max(0, pos0 - g.window + 1) : 0;
-  const int blk0 = kmin / KV_BLOCK, blk1 = pos_last / KV_BLOCK;
+  int blk0 = kmin / KV_BLOCK, blk1 = pos_last / KV_BLOCK;
+  // split launches (n_splits > 1, decode-shaped steps): CTA z takes the blocks of ONE fixed split -- LATENT_SPLIT_BLOCKS
+  // consecutive blocks, boundaries at multiples of it in the sequence's own block numbering -- and leaves an unnormalised
+  // partial (acc, m, l) per pair for latent_attn_merge_kernel
+  float* my_part = nullptr;
+  if (n_splits > 1) {
+    my_part = part + ((((size_t)blockIdx.x * gridDim.y + blockIdx.y) * n_splits + blockIdx.z) * LATENT_PAIRS) * (R + 2);
+    const int s_abs = blk0 / LATENT_SPLIT_BLOCKS + blockIdx.z;
+    blk0 = max(blk0, s_abs * LATENT_SPLIT_BLOCKS);
+    blk1 = min(blk1, s_abs * LATENT_SPLIT_BLOCKS + LATENT_SPLIT_BLOCKS - 1);
+    if (blk0 > blk1) {  // nothing in this split (CTA-uniform): an empty partial
+      if (tid < npairs) {
+        my_part[(size_t)tid * (R + 2) + R] = -FLT_MAX;
+        my_part[(size_t)tid * (R + 2) + R + 1] = 0.f;
+      }
+      return;
+    }
+  }
   const int32_t* bt = block_table + (size_t)sq.block_row * bt_stride;
   const int chunks_per_row = D / 8;
   auto load_block = [&](int blk, int st) {
@@ -386,6 +405,29 @@ latent_attn_mma_kernel(const float* __restrict__ q_abs, const __nv_bfloat16* __r
       }
     }
   }
+  if (my_part != nullptr) {
+    if (lane == 0)
+#pragma unroll
+      for (int u = 0; u < 2; ++u)
+        if (on[u]) {
+          my_part[(size_t)prow[u] * (R + 2) + R] = m_run[u];
+          my_part[(size_t)prow[u] * (R + 2) + R + 1] = l_run[u];
+        }
+#pragma unroll
+    for (int hf = 0; hf < 2; ++hf) {
+      const int p = gq + hf * 8;
+      if (p >= npairs) continue;
+#pragma unroll
+      for (int j = 0; j < NT; ++j) {
+        const int n = (warp + LAT_WARPS * j) * 8 + t2;
+        if (n < R) {
+          my_part[(size_t)p * (R + 2) + n] = acc[j][hf * 2];
+          my_part[(size_t)p * (R + 2) + n + 1] = acc[j][hf * 2 + 1];
+        }
+      }
+    }
+    return;
+  }
   if (lane == 0) {
     if (on[0]) l_s[prow[0]] = l_run[0];
     if (on[1]) l_s[prow[1]] = l_run[1];
@@ -409,10 +451,61 @@ latent_attn_mma_kernel(const float* __restrict__ q_abs, const __nv_bfloat16* __r
   }
 }
 
+// o_lat[pair] = sum_z e^(m_z - M) acc_z / sum_z e^(m_z - M) l_z over the splits in ascending order, M = max_z m_z.
+// One CTA per (tile, head group, pair); the split weights are worked out once in shared memory.
+constexpr int LATENT_MAX_SPLITS = 64;
+__global__ void __launch_bounds__(LAT_THREADS)
+latent_attn_merge_kernel(const float* __restrict__ part, int n_splits, const AttnSeq* __restrict__ seqs,
+                         const LatentTile* __restrict__ tiles, void* __restrict__ o_lat, int o_dtype, LatentGeom g) {
+  __shared__ float w_s[LATENT_MAX_SPLITS];
+  __shared__ float inv_s;
+  griddep_launch();
+  griddep_wait();
+  const int R = g.kv_rank;
+  const LatentTile tile = tiles[blockIdx.x];
+  const AttnSeq sq = seqs[tile.seq];
+  const int h0 = blockIdx.y * LATENT_PAIRS;
+  const int nh = min(g.heads - h0, LATENT_PAIRS);
+  const int p = blockIdx.z;
+  if (p >= tile.nq * nh) return;
+  const float* base = part + (((size_t)blockIdx.x * gridDim.y + blockIdx.y) * n_splits * LATENT_PAIRS + p) * (R + 2);
+  const size_t zs = (size_t)LATENT_PAIRS * (R + 2);  // floats between consecutive splits of one pair
+  if (threadIdx.x < 32) {  // one warp: lane z, z + 32 (n_splits <= 64)
+    float m[2], l[2];
+#pragma unroll
+    for (int u = 0; u < 2; ++u) {
+      const int z = threadIdx.x + 32 * u;
+      l[u] = z < n_splits ? base[z * zs + R + 1] : 0.f;
+      m[u] = l[u] > 0.f ? base[z * zs + R] : -FLT_MAX;
+    }
+    const float M = warp_max_f(fmaxf(m[0], m[1]));
+    float den = 0.f;
+#pragma unroll
+    for (int u = 0; u < 2; ++u) {
+      const float w = l[u] > 0.f ? expf(m[u] - M) : 0.f;
+      if (threadIdx.x + 32 * u < n_splits) w_s[threadIdx.x + 32 * u] = w;
+      den += w * l[u];
+    }
+    den = warp_sum_f(den);
+    if (threadIdx.x == 0) inv_s = 1.f / den;
+  }
+  __syncthreads();
+  const int tq = p / nh, h = h0 + p - tq * nh;
+  const size_t o = ((size_t)(sq.q_start + tile.q0 + tq) * g.heads + h) * R;
+  for (int d = threadIdx.x; d < R; d += LAT_THREADS) {
+    float num = 0.f;
+    for (int z = 0; z < n_splits; ++z) {
+      const float w = w_s[z];
+      if (w > 0.f) num = fmaf(w, base[z * zs + d], num);
+    }
+    st_any(o_lat, o_dtype, o + d, num * inv_s);
+  }
+}
+
 template <int NT>
 cudaError_t launch_attn_mma(const float* q_abs, const void* cache, const AttnSeq* seqs, const LatentTile* tiles, int n_tiles,
                             const int32_t* block_table, int bt_stride, void* o_lat, int o_dtype, const LatentGeom& g,
-                            cudaStream_t stream) {
+                            cudaStream_t stream, float* part = nullptr, int n_splits = 1) {
   const size_t smem = lat_mma_smem(g.row());
   static size_t attr_bytes = 0;
   if (smem > 48 * 1024 && smem > attr_bytes) {
@@ -420,9 +513,13 @@ cudaError_t launch_attn_mma(const float* q_abs, const void* cache, const AttnSeq
     if (e != cudaSuccess) return e;
     attr_bytes = smem;
   }
-  const dim3 grid(n_tiles, (g.heads + LATENT_PAIRS - 1) / LATENT_PAIRS);
-  return launch_k(latent_attn_mma_kernel<NT>, grid, dim3(LAT_THREADS), smem, stream, q_abs,
-                  reinterpret_cast<const __nv_bfloat16*>(cache), seqs, tiles, block_table, bt_stride, o_lat, o_dtype, g);
+  const dim3 grid(n_tiles, (g.heads + LATENT_PAIRS - 1) / LATENT_PAIRS, n_splits);
+  const cudaError_t e = launch_k(latent_attn_mma_kernel<NT>, grid, dim3(LAT_THREADS), smem, stream, q_abs,
+                                 reinterpret_cast<const __nv_bfloat16*>(cache), seqs, tiles, block_table, bt_stride, o_lat,
+                                 o_dtype, g, part, n_splits);
+  if (e != cudaSuccess || n_splits <= 1) return e;
+  return launch_k(latent_attn_merge_kernel, dim3(grid.x, grid.y, LATENT_PAIRS), dim3(LAT_THREADS), 0, stream,
+                  (const float*)part, n_splits, seqs, tiles, o_lat, o_dtype, g);
 }
 
 bool latent_mma_eligible(const void* cache, int dtype, const LatentGeom& g) {
@@ -487,12 +584,31 @@ cudaError_t latent_q_rope_launch(const void* q, int q_dtype, const LatentGeom& g
 
 cudaError_t latent_attn_launch(const float* q_abs, const void* cache, int dtype, const AttnSeq* seqs,
                                const LatentTile* tiles, int n_tiles, const int32_t* block_table, int bt_stride,
-                               void* o_lat, int o_dtype, const LatentGeom& g, cudaStream_t stream) {
+                               void* o_lat, int o_dtype, const LatentGeom& g, cudaStream_t stream, float* split_ws,
+                               size_t split_ws_floats, int max_kv_len, int num_sms) {
   if (n_tiles <= 0) return cudaSuccess;
   if (latent_mma_eligible(cache, dtype, g)) {
-    if (g.kv_rank <= 128) return launch_attn_mma<2>(q_abs, cache, seqs, tiles, n_tiles, block_table, bt_stride, o_lat, o_dtype, g, stream);
-    if (g.kv_rank <= 256) return launch_attn_mma<4>(q_abs, cache, seqs, tiles, n_tiles, block_table, bt_stride, o_lat, o_dtype, g, stream);
-    return launch_attn_mma<8>(q_abs, cache, seqs, tiles, n_tiles, block_table, bt_stride, o_lat, o_dtype, g, stream);
+    // Steps with too few tiles to fill the GPU (decode-shaped): every tile's key range is cut into fixed splits that run as
+    // CTAs of their own.  The split count is a function of the longest sequence rounded up to whole splits (and of the
+    // window), so a captured launch stays valid for every step of its CUDA-graph key.
+    int n_splits = 1;
+    const int hg = (g.heads + LATENT_PAIRS - 1) / LATENT_PAIRS;
+    static int split_on = -1;
+    if (split_on < 0) {
+      const char* e = getenv("TGIS_LATENT_ATTN_SPLIT");
+      split_on = (e && e[0] == '0') ? 0 : 1;
+    }
+    if (split_on && split_ws != nullptr && n_tiles * hg < num_sms) {
+      const int split_keys = LATENT_SPLIT_BLOCKS * KV_BLOCK;
+      int span = (max_kv_len + split_keys - 1) / split_keys * split_keys;
+      if (g.window > 0) span = std::min(span, (g.window + LATENT_PAIRS + split_keys - 1) / split_keys * split_keys);
+      const int z = span / split_keys + 1;
+      if (z > 2 && z <= LATENT_MAX_SPLITS && (size_t)n_tiles * hg * z * LATENT_PAIRS * (g.kv_rank + 2) <= split_ws_floats)
+        n_splits = z;
+    }
+    if (g.kv_rank <= 128) return launch_attn_mma<2>(q_abs, cache, seqs, tiles, n_tiles, block_table, bt_stride, o_lat, o_dtype, g, stream, split_ws, n_splits);
+    if (g.kv_rank <= 256) return launch_attn_mma<4>(q_abs, cache, seqs, tiles, n_tiles, block_table, bt_stride, o_lat, o_dtype, g, stream, split_ws, n_splits);
+    return launch_attn_mma<8>(q_abs, cache, seqs, tiles, n_tiles, block_table, bt_stride, o_lat, o_dtype, g, stream, split_ws, n_splits);
   }
   if (dtype == DT_BF16)
     return launch_attn_ct<__nv_bfloat16>(q_abs, cache, seqs, tiles, n_tiles, block_table, bt_stride, o_lat, o_dtype, g, stream);

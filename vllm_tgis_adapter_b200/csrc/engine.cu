@@ -262,7 +262,9 @@ struct tgis_engine {
         *pnx_qabs = nullptr, *pnx_o = nullptr, *pnx_rl = nullptr, *pnx_mixw = nullptr, *pnx_sgate = nullptr,
         *pnx_yS = nullptr, *pnx_yE = nullptr;
   int32_t *pnx_ids = nullptr, *pnx_segoff = nullptr, *pnx_order = nullptr, *pnx_inv = nullptr;
-  int pnx_tile_tokens = 1, step_n_ltiles = 0;
+  int pnx_tile_tokens = 1, step_n_ltiles = 0, step_max_kv = 0;
+  float* pnx_attn_ws = nullptr;                      // split partials of decode-shaped attention launches
+  size_t pnx_attn_ws_floats = 0;
   size_t off_ltiles = 0;
   int logit_rows_cap = 0;                            // rows of the logits buffer (>= max_num_seqs)
   int logits_ld = 0;                                 // its row length: the vocabulary rounded up to the sampler's 8-column
@@ -1241,6 +1243,10 @@ struct tgis_engine {
     pnx_actE = pnx_alloc_dt(T * m_top * m_ff, true);
     pnx_yE = pnx_alloc<float>(T * m_top * W);
     pnx_last = pnx_alloc_dt(std::max<size_t>(logit_rows_cap, T) * W, true);
+    if (pnx_dt == DT_BF16) {
+      pnx_attn_ws_floats = (size_t)8 << 20;  // 32 MB
+      pnx_attn_ws = pnx_alloc<float>(pnx_attn_ws_floats);
+    }
     // paged cache of latent rows: the block ids of the engine's block manager index every layer's cache
     size_t kv_bytes = c.kv_cache_bytes;
     if (kv_bytes == 0) {
@@ -1337,7 +1343,8 @@ struct tgis_engine {
     return fail("unknown layer weight " + name);
   }
 
-  // Dense Y = X W^T.  bf16 operands in the tcgen05 kernel's layout (whole 64-element k-blocks, at least one full weight tile)
+  // Dense Y = X W^T.  bf16 operands in the tcgen05 kernel's layout (whole 64-element k-blocks, at least four of them -- the
+  // range its stream-K schedules are tested in --, at least one full weight tile)
   // go to that kernel -- fp32 accumulators out, or SwiGLU fused over interleaved gate / up rows --, everything else to the
   // general kernel.  Tensor maps are made on first use and kept (one per weight; one per activation buffer, width and
   // token-tile height).  TGIS_PNX_TC=0: general kernel only.
@@ -1366,8 +1373,8 @@ struct tgis_engine {
   }
   void pnx_gemm(const void* X, int x_dt, int ldx, const void* Wt, void* Y, int y_dt, int ldy, int T, int N, int K,
                 int mode = GEMM_ANY_PLAIN, bool x_tma_ok = true) {
-    if (pnx_tc && x_tma_ok && pnx_dt == DT_BF16 && x_dt == DT_BF16 && ldx == K && K % 64 == 0 && N % 8 == 0 && N >= 128 &&
-        !cfg.debug_gemm_ref) {
+    if (pnx_tc && x_tma_ok && pnx_dt == DT_BF16 && x_dt == DT_BF16 && ldx == K && K % 64 == 0 && K >= 256 && N % 8 == 0 &&
+        N >= 128 && !cfg.debug_gemm_ref) {
       const int out_mode = mode == GEMM_ANY_SWIGLU && y_dt == DT_BF16 ? 2 : mode == GEMM_ANY_PLAIN ? (y_dt == DT_F32 ? 1 : 0) : -1;
       if (out_mode >= 0 && pnx_gemm_tc(X, Wt, Y, ldy, T, N, K, out_mode)) return;
     }
@@ -1414,7 +1421,8 @@ struct tgis_engine {
         a.batch = H; a.x_bs = hd; a.w_bs = (long long)s.kv_rank * s.dim; a.y_bs = D;
         CK(gemm_any_launch(a, stream));
       }
-      CK(latent_attn_launch(pnx_qabs, l.cache, A, d_seqs, d_tiles, step_n_ltiles, d_bt, bt_stride, pnx_olat, A, g, stream));
+      CK(latent_attn_launch(pnx_qabs, l.cache, A, d_seqs, d_tiles, step_n_ltiles, d_bt, bt_stride, pnx_olat, A, g, stream,
+                            pnx_attn_ws, pnx_attn_ws_floats, step_max_kv, num_sms));
       {  // o_h = gate_h * W_uv,h o_lat_h
         GemmAny a{};
         a.X = pnx_olat; a.W = l.w_uv; a.Y = pnx_oA;
@@ -1918,10 +1926,12 @@ struct tgis_engine {
     int32_t* bt = hs<int32_t>(off_bt);
     const int S = (int)batch.size();
     step_n_ltiles = 0;
+    step_max_kv = 0;
     for (int s = 0; s < S; ++s) {
       Request& r = *batch[s].r;
       const int q_len = batch[s].q_len;
       const int kv_len = r.n_computed + q_len;
+      step_max_kv = std::max(step_max_kv, kv_len);
       seqs[s] = AttnSeq{T, q_len, kv_len, s};
       memcpy(bt + (size_t)s * bt_stride, r.blocks.data(), sizeof(int32_t) * r.blocks.size());
       for (int j = 0; j < q_len; ++j) {

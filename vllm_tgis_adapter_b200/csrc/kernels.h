@@ -313,9 +313,13 @@ struct LatentTile {  // one CTA's queries: tokens [q0, q0 + nq) of the step's se
 constexpr int LATENT_PAIRS = 16;  // (token, head) pairs per CTA
 inline int latent_tile_tokens(int heads) { return heads >= LATENT_PAIRS ? 1 : LATENT_PAIRS / heads; }
 // q_abs fp32 [T, heads, row()], cache DT_* [num_blocks][KV_BLOCK][row()], o_lat DT_* [T, heads, kv_rank]
+// split_ws (optional, fp32): with it, steps of few tiles cut every tile's keys into fixed splits of LATENT_SPLIT_BLOCKS cache
+// blocks that run as CTAs of their own and are merged by a second kernel; max_kv_len: the longest sequence of the step
+constexpr int LATENT_SPLIT_BLOCKS = 4;
 cudaError_t latent_attn_launch(const float* q_abs, const void* cache, int dtype, const AttnSeq* seqs,
                                const LatentTile* tiles, int n_tiles, const int32_t* block_table, int bt_stride,
-                               void* o_lat, int o_dtype, const LatentGeom& g, cudaStream_t stream);
+                               void* o_lat, int o_dtype, const LatentGeom& g, cudaStream_t stream, float* split_ws = nullptr,
+                               size_t split_ws_floats = 0, int max_kv_len = 0, int num_sms = 148);
 
 // ---- moe.cu: top-k router and the bookkeeping of the grouped expert products ----------------------------------------
 // logits fp32 [T, ld] (columns [0, E): experts; column E, when side_gate != nullptr: the shared expert's gate logit):

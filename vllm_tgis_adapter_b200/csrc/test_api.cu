@@ -582,7 +582,13 @@ int tgis_k_latent_attn(const float* q_abs, const void* cache, int32_t dt, const 
   KCK(d_seqs.upload(seqs.data(), seqs.size()));
   KCK(d_tiles.upload(tiles.data(), tiles.size()));
   KCK(d_bt.upload(block_table_host, (size_t)bt_rows * bt_stride));
-  KCK(latent_attn_launch(q_abs, cache, dt, d_seqs.p, d_tiles.p, (int)tiles.size(), d_bt.p, bt_stride, o_lat, o_dt, geom, 0));
+  Tmp<float> ws;              // split partials (only decode-shaped launches over bf16 rows use them)
+  const size_t ws_floats = (size_t)4 << 20;
+  KCK(ws.alloc(ws_floats));
+  int max_kv = 0;
+  for (const AttnSeq& s : seqs) max_kv = std::max(max_kv, s.kv_len);
+  KCK(latent_attn_launch(q_abs, cache, dt, d_seqs.p, d_tiles.p, (int)tiles.size(), d_bt.p, bt_stride, o_lat, o_dt, geom, 0,
+                         ws.p, ws_floats, max_kv, test_num_sms()));
   KCK(cudaDeviceSynchronize());
   return 0;
 }
