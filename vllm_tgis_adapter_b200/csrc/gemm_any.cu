@@ -10,7 +10,9 @@
 // Every output element is the sum over k = 0 .. K-1 in ascending order inside one thread, so a row's result depends
 // neither on the other rows of the launch nor on where in a segment it landed.
 //
-// Two kernels: bf16 operands whose rows start on 16-byte boundaries run on the tensor cores (gemm_any_mma_kernel below);
+// Three kernels: a handful of outputs over long rows (router and gate projections of a decode step) take one warp per
+// output (gemm_any_rowdot_kernel); bf16 operands whose rows start on 16-byte boundaries run on the tensor cores
+// (gemm_any_mma_kernel);
 // everything else -- fp32 operands, odd leading dimensions -- runs on the FMA pipe (a [16 TM x 64] tile per 256-thread CTA,
 // TM x 4 outputs per thread, k-blocks of 16 staged through shared memory).  Dense launches that fit the tcgen05 kernel's
 // operand layout are routed there by the engine.
@@ -324,6 +326,36 @@ bool mma_eligible(const GemmAny& a) {
          a.x_bs % 8 == 0 && a.w_bs % 8 == 0 && a.w_gs % 8 == 0 && al16(a.X) && al16(a.W);
 }
 
+// ---- few outputs, long rows (a router or gate projection in a decode step): one warp per output element -------------
+// lanes stride the reduction (coalesced), fixed shuffle tree at the end; any alignment, any operand types.
+template <class XT, class WT>
+__global__ void __launch_bounds__(ANY_THREADS) gemm_any_rowdot_kernel(GemmAny a) {
+  griddep_launch();
+  griddep_wait();
+  const int lane = threadIdx.x & 31;
+  const long long out = (long long)blockIdx.x * (ANY_THREADS / 32) + (threadIdx.x >> 5);
+  if (out >= (long long)a.T * a.N) return;
+  const int t = (int)(out / a.N), n = (int)(out % a.N);
+  const XT* x = reinterpret_cast<const XT*>(a.X) + (size_t)t * a.ldx;
+  const WT* w = reinterpret_cast<const WT*>(a.W) + (size_t)n * a.ldw;
+  float acc = 0.f;
+#pragma unroll 4
+  for (int k = lane; k < a.K; k += 32) acc = fmaf(ld_as_float(x + k), ld_as_float(w + k), acc);
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
+  if (lane == 0) reinterpret_cast<float*>(a.Y)[(size_t)t * a.ldy + n] = acc;
+}
+bool rowdot_eligible(const GemmAny& a) {
+  return a.seg_off == nullptr && a.batch <= 1 && a.mode == GEMM_ANY_PLAIN && a.y_dtype == DT_F32 && a.N < 128 &&
+         (long long)a.T * a.N <= 8192 && a.K >= 256 && !(a.x_dtype == DT_BF16 && a.w_dtype == DT_F32);
+}
+template <class XT, class WT>
+cudaError_t launch_rowdot(const GemmAny& a, cudaStream_t stream) {
+  const long long outs = (long long)a.T * a.N;
+  return launch_k(gemm_any_rowdot_kernel<XT, WT>, dim3((unsigned)((outs + ANY_THREADS / 32 - 1) / (ANY_THREADS / 32))),
+                  dim3(ANY_THREADS), 0, stream, a);
+}
+
 template <class XT, class WT, class OT>
 cudaError_t launch_tm(const GemmAny& a, cudaStream_t stream) {
   // rows per tile: 16 for skinny problems (decode steps, small expert segments), 64 otherwise
@@ -345,6 +377,10 @@ cudaError_t gemm_any_launch(const GemmAny& a, cudaStream_t stream) {
   if (a.mode == GEMM_ANY_ROWSCALE && a.row_scale == nullptr) return cudaErrorInvalidValue;
   if (a.gather != nullptr && a.gather_div <= 0) return cudaErrorInvalidValue;
   using bf = __nv_bfloat16;
+  if (rowdot_eligible(a)) {
+    if (a.x_dtype == DT_BF16) return launch_rowdot<bf, bf>(a, stream);
+    return a.w_dtype == DT_BF16 ? launch_rowdot<float, bf>(a, stream) : launch_rowdot<float, float>(a, stream);
+  }
   if (mma_eligible(a)) return a.y_dtype == DT_BF16 ? launch_mma<bf>(a, stream) : launch_mma<float>(a, stream);
   const int key = a.x_dtype * 4 + a.w_dtype * 2 + a.y_dtype;  // DT_F32 = 0, DT_BF16 = 1
   switch (key) {
