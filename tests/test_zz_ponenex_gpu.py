@@ -64,7 +64,8 @@ def _gemm_any(x, w, y, T, N, K, *, ldx=None, ldw=None, ldy=None, batch=1, x_bs=0
     torch.cuda.synchronize()
 
 
-@pytest.mark.parametrize("T,N,K", [(1, 5, 200), (5, 17, 33), (70, 130, 88), (200, 64, 100), (3, 440, 7)])
+@pytest.mark.parametrize("T,N,K", [(1, 5, 200), (5, 17, 33), (70, 130, 88), (200, 64, 100), (3, 440, 7), (7, 65, 2048), (1, 17, 264),
+                                   (3, 9, 301)])
 @pytest.mark.parametrize("dt", [torch.float32, torch.bfloat16])
 def test_gemm_any_dense_any_shape(T, N, K, dt):
     g = torch.Generator().manual_seed(T * 1000 + N)

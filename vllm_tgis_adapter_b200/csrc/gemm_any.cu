@@ -328,7 +328,7 @@ bool mma_eligible(const GemmAny& a) {
 
 // ---- few outputs, long rows (a router or gate projection in a decode step): one warp per output element -------------
 // lanes stride the reduction (coalesced), fixed shuffle tree at the end; any alignment, any operand types.
-template <class XT, class WT>
+template <class XT, class WT, bool VEC8>
 __global__ void __launch_bounds__(ANY_THREADS) gemm_any_rowdot_kernel(GemmAny a) {
   griddep_launch();
   griddep_wait();
@@ -339,8 +339,25 @@ __global__ void __launch_bounds__(ANY_THREADS) gemm_any_rowdot_kernel(GemmAny a)
   const XT* x = reinterpret_cast<const XT*>(a.X) + (size_t)t * a.ldx;
   const WT* w = reinterpret_cast<const WT*>(a.W) + (size_t)n * a.ldw;
   float acc = 0.f;
+  if (VEC8) {  // bf16 rows on 16-byte boundaries, K % 8 == 0: 8 elements per load, several loads in flight
+    const uint4* x4 = reinterpret_cast<const uint4*>(x);
+    const uint4* w4 = reinterpret_cast<const uint4*>(w);
+#pragma unroll 8
+    for (int c = lane; c < a.K / 8; c += 32) {
+      const uint4 xv = x4[c], wv = w4[c];
+      const __nv_bfloat162* xp = reinterpret_cast<const __nv_bfloat162*>(&xv);
+      const __nv_bfloat162* wp = reinterpret_cast<const __nv_bfloat162*>(&wv);
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        const float2 xf = __bfloat1622float2(xp[e]), wf = __bfloat1622float2(wp[e]);
+        acc = fmaf(xf.x, wf.x, acc);
+        acc = fmaf(xf.y, wf.y, acc);
+      }
+    }
+  } else {
 #pragma unroll 4
-  for (int k = lane; k < a.K; k += 32) acc = fmaf(ld_as_float(x + k), ld_as_float(w + k), acc);
+    for (int k = lane; k < a.K; k += 32) acc = fmaf(ld_as_float(x + k), ld_as_float(w + k), acc);
+  }
 #pragma unroll
   for (int o = 16; o > 0; o >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
   if (lane == 0) reinterpret_cast<float*>(a.Y)[(size_t)t * a.ldy + n] = acc;
@@ -349,10 +366,10 @@ bool rowdot_eligible(const GemmAny& a) {
   return a.seg_off == nullptr && a.batch <= 1 && a.mode == GEMM_ANY_PLAIN && a.y_dtype == DT_F32 && a.N < 128 &&
          (long long)a.T * a.N <= 8192 && a.K >= 256 && !(a.x_dtype == DT_BF16 && a.w_dtype == DT_F32);
 }
-template <class XT, class WT>
+template <class XT, class WT, bool VEC8 = false>
 cudaError_t launch_rowdot(const GemmAny& a, cudaStream_t stream) {
   const long long outs = (long long)a.T * a.N;
-  return launch_k(gemm_any_rowdot_kernel<XT, WT>, dim3((unsigned)((outs + ANY_THREADS / 32 - 1) / (ANY_THREADS / 32))),
+  return launch_k(gemm_any_rowdot_kernel<XT, WT, VEC8>, dim3((unsigned)((outs + ANY_THREADS / 32 - 1) / (ANY_THREADS / 32))),
                   dim3(ANY_THREADS), 0, stream, a);
 }
 
@@ -378,7 +395,11 @@ cudaError_t gemm_any_launch(const GemmAny& a, cudaStream_t stream) {
   if (a.gather != nullptr && a.gather_div <= 0) return cudaErrorInvalidValue;
   using bf = __nv_bfloat16;
   if (rowdot_eligible(a)) {
-    if (a.x_dtype == DT_BF16) return launch_rowdot<bf, bf>(a, stream);
+    if (a.x_dtype == DT_BF16) {
+      const bool vec = a.K % 8 == 0 && a.ldx % 8 == 0 && a.ldw % 8 == 0 && (reinterpret_cast<uintptr_t>(a.X) & 15) == 0 &&
+                       (reinterpret_cast<uintptr_t>(a.W) & 15) == 0;
+      return vec ? launch_rowdot<bf, bf, true>(a, stream) : launch_rowdot<bf, bf>(a, stream);
+    }
     return a.w_dtype == DT_BF16 ? launch_rowdot<float, bf>(a, stream) : launch_rowdot<float, float>(a, stream);
   }
   if (mma_eligible(a)) return a.y_dtype == DT_BF16 ? launch_mma<bf>(a, stream) : launch_mma<float>(a, stream);
