@@ -772,7 +772,7 @@ def run_ours(args) -> dict | None:
 # ------------------------------------------------------------------------------------------------ --arch-compare
 # Prefill and decode throughput of the Ponenex family beside the closest existing family (Llama) at equal hidden size, layer
 # count and active feed-forward width, random weights, device-timed (the engine's CUDA events around every step).  Not the
-# default workload: `python bench.py --arch-compare` prints its own JSON line and leaves the contract line alone.
+# default workload: `python bench.py --arch-compare` prints its own JSON line; the default JSON line is untouched.
 ARCH_COMPARE = [("ponenex-1k", "llama-cmp-1k"), ("ponenex-2k", "llama-cmp-2k")]
 
 
