@@ -585,7 +585,8 @@ cudaError_t latent_q_rope_launch(const void* q, int q_dtype, const LatentGeom& g
 cudaError_t latent_attn_launch(const float* q_abs, const void* cache, int dtype, const AttnSeq* seqs,
                                const LatentTile* tiles, int n_tiles, const int32_t* block_table, int bt_stride,
                                void* o_lat, int o_dtype, const LatentGeom& g, cudaStream_t stream, float* split_ws,
-                               size_t split_ws_floats, int max_kv_len, int num_sms) {
+                               size_t split_ws_floats, int max_kv_len, int num_sms, int* n_launched) {
+  if (n_launched) *n_launched = n_tiles > 0 ? 1 : 0;
   if (n_tiles <= 0) return cudaSuccess;
   if (latent_mma_eligible(cache, dtype, g)) {
     // Steps with too few tiles to fill the GPU (decode-shaped): every tile's key range is cut into fixed splits that run as
@@ -606,6 +607,7 @@ cudaError_t latent_attn_launch(const float* q_abs, const void* cache, int dtype,
       if (z > 2 && z <= LATENT_MAX_SPLITS && (size_t)n_tiles * hg * z * LATENT_PAIRS * (g.kv_rank + 2) <= split_ws_floats)
         n_splits = z;
     }
+    if (n_launched && n_splits > 1) *n_launched = 2;  // + the merge kernel
     if (g.kv_rank <= 128) return launch_attn_mma<2>(q_abs, cache, seqs, tiles, n_tiles, block_table, bt_stride, o_lat, o_dtype, g, stream, split_ws, n_splits);
     if (g.kv_rank <= 256) return launch_attn_mma<4>(q_abs, cache, seqs, tiles, n_tiles, block_table, bt_stride, o_lat, o_dtype, g, stream, split_ws, n_splits);
     return launch_attn_mma<8>(q_abs, cache, seqs, tiles, n_tiles, block_table, bt_stride, o_lat, o_dtype, g, stream, split_ws, n_splits);

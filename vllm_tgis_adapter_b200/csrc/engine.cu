@@ -1421,8 +1421,10 @@ struct tgis_engine {
         a.batch = H; a.x_bs = hd; a.w_bs = (long long)s.kv_rank * s.dim; a.y_bs = D;
         CK(gemm_any_launch(a, stream));
       }
+      int attn_launches = 0;
       CK(latent_attn_launch(pnx_qabs, l.cache, A, d_seqs, d_tiles, step_n_ltiles, d_bt, bt_stride, pnx_olat, A, g, stream,
-                            pnx_attn_ws, pnx_attn_ws_floats, step_max_kv, num_sms));
+                            pnx_attn_ws, pnx_attn_ws_floats, step_max_kv, num_sms, &attn_launches));
+      n_launches += attn_launches - 1;  // (one attention launch is part of the count below)
       {  // o_h = gate_h * W_uv,h o_lat_h
         GemmAny a{};
         a.X = pnx_olat; a.W = l.w_uv; a.Y = pnx_oA;

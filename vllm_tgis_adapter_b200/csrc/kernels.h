@@ -319,7 +319,7 @@ constexpr int LATENT_SPLIT_BLOCKS = 4;
 cudaError_t latent_attn_launch(const float* q_abs, const void* cache, int dtype, const AttnSeq* seqs,
                                const LatentTile* tiles, int n_tiles, const int32_t* block_table, int bt_stride,
                                void* o_lat, int o_dtype, const LatentGeom& g, cudaStream_t stream, float* split_ws = nullptr,
-                               size_t split_ws_floats = 0, int max_kv_len = 0, int num_sms = 148);
+                               size_t split_ws_floats = 0, int max_kv_len = 0, int num_sms = 148, int* n_launched = nullptr);
 
 // ---- moe.cu: top-k router and the bookkeeping of the grouped expert products ----------------------------------------
 // logits fp32 [T, ld] (columns [0, E): experts; column E, when side_gate != nullptr: the shared expert's gate logit):
