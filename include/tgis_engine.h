@@ -39,7 +39,7 @@
 extern "C" {
 #endif
 
-#define TGIS_ABI_VERSION 8
+#define TGIS_ABI_VERSION 9
 #define TGIS_MAX_REQUEST_ID 96
 #define TGIS_MAX_TOPN 12 /* reference forces max_logprobs >= 11: tgis_utils/args.py:214-216 */
 #define TGIS_MAX_STOP_TOKEN_IDS 8
@@ -62,6 +62,14 @@ typedef struct tgis_engine tgis_engine;
  *          mixture-of-experts feed-forward (biased top-k router, softmax over the chosen logits, gated shared expert).
  *          Created with tgis_engine_create_spec; bf16 or fp32 operands.  Single GPU, no LoRA slots. */
 #define TGIS_ARCH_PONENEX 2
+
+/*   FALERAX: a layer list as well (tgis_engine_create_spec), fp32 residual stream, sublayers that read the stream itself
+ *          and are normed on their OUTPUT only (x += rmsnorm(sublayer(x)) * w, TGIS_STYLE_POST_NORM), logits from the
+ *          embedding table (TGIS_STYLE_TIED_HEAD).  Mixers: softcapped grouped-query attention beside a gated matrix
+ *          memory (TGIS_MIXER_PARALLEL), selective scan (TGIS_MIXER_SELECTIVE_SCAN), decayed outer-product memory with
+ *          token shift (TGIS_MIXER_WKV); dense GeGLU feed-forward.  The recurrent mixers keep fp32 state per sequence slot.
+ *          bf16 or fp32 operands.  Single GPU, no LoRA slots. */
+#define TGIS_ARCH_FALERAX 3
 
 /* Model + runtime configuration (bf16 decoder-only transformer; see TGIS_ARCH_*). */
 typedef struct tgis_config {
@@ -104,8 +112,12 @@ typedef struct tgis_config {
 /* Per-layer geometry for architectures whose layers are listed one by one (TGIS_ARCH_PONENEX); tgis_config carries hidden,
  * vocab, max_model_len and the runtime limits, its head / ffn / rope fields are unused. */
 #define TGIS_MIXER_LATENT_ATTENTION 1
+#define TGIS_MIXER_PARALLEL 2        /* softcapped attention and a gated matrix memory on the same input, averaged */
+#define TGIS_MIXER_SELECTIVE_SCAN 3  /* short causal convolution + input-dependent state-space scan */
+#define TGIS_MIXER_WKV 4             /* token shift + per-channel decayed outer-product memory with a current-token bonus */
 #define TGIS_MLP_NONE 0
 #define TGIS_MLP_MOE 1
+#define TGIS_MLP_DENSE_GELU 2        /* down(gelu_tanh(gate h) * (up h)), width `ff` */
 typedef struct tgis_layer_spec {
   int32_t mixer;        /* TGIS_MIXER_* */
   int32_t heads, dim, rot_dim, vdim, kv_rank, q_rank; /* per head: dim unrotated + rot_dim rotated query/key dims, vdim values */
@@ -116,8 +128,25 @@ typedef struct tgis_layer_spec {
   int32_t mlp;          /* TGIS_MLP_* */
   int32_t experts, top, expert_ff;
   int32_t shared_ff;    /* 0: no shared expert */
+  int32_t ff;           /* TGIS_MLP_DENSE_GELU */
+  /* TGIS_MIXER_PARALLEL, attention side: heads query heads of `dim`, kv_heads key/value heads (values of `vdim`), `scale`;
+   * score <- softcap * tanh(score / softcap) (softcap <= 0: none); the query is multiplied by
+   * 1 + qt_coef * ln(floor((pos + 1) / qt_every) + 1) (qt_every <= 0: no temperature) */
+  int32_t kv_heads;
+  float softcap, qt_coef;
+  int32_t qt_every;
+  /* ... matrix-memory side: mm_heads heads, keys / queries of mm_dim, values of mm_vdim, log gates capped at gate_cap */
+  int32_t mm_heads, mm_dim, mm_vdim;
+  float gate_cap;
+  /* TGIS_MIXER_SELECTIVE_SCAN: `inner` channels with `state` entries each, step-size rank, convolution taps */
+  int32_t inner, state, dt_rank, conv;
+  /* TGIS_MIXER_WKV: heads x dim (keys and values alike); rank of the decay's low-rank map */
+  int32_t decay_rank;
   int32_t reserved;
 } tgis_layer_spec;
+#define TGIS_STYLE_POST_NORM 1 /* x += rmsnorm(sublayer(x)) * w with a plain weight; unset: pre- and post-norm, weights stored
+                                * as deviations from one */
+#define TGIS_STYLE_TIED_HEAD 2 /* logits = embedding table x (no "head" tensor) */
 #define TGIS_DTYPE_BF16 0 /* bf16 operands, fp32 accumulation; norms, softmax, routers and the residual sum in fp32 */
 #define TGIS_DTYPE_F32 1  /* everything in true fp32 (no TF32) */
 typedef struct tgis_model_spec {
@@ -126,7 +155,7 @@ typedef struct tgis_model_spec {
   float embed_scale;    /* x = embed[token] * embed_scale */
   float residual_mult;  /* x += residual_mult * post_norm(sublayer(pre_norm(x))) */
   float norm_eps;
-  int32_t reserved;
+  int32_t style;        /* TGIS_STYLE_* bits */
   const tgis_layer_spec* layers; /* [n_layers] */
 } tgis_model_spec;
 
@@ -229,10 +258,14 @@ const char* tgis_last_error(void);
 int tgis_abi_version(void);
 
 int tgis_engine_create(const tgis_config* cfg, tgis_engine** out);
-/* cfg->arch == TGIS_ARCH_PONENEX; parameter names: "embed", "head", "final.norm", "l<i>.norm1|norm1b|norm2|norm2b",
+/* Layer-list architectures.  cfg->arch == TGIS_ARCH_PONENEX; parameter names: "embed", "head", "final.norm", "l<i>.norm1|norm1b|norm2|norm2b",
  * "l<i>.mix.dq|dq.norm|uq|dkv|dkv.norm|uk|uv|g|o", "l<i>.mlp.router|router.b|e<j>.gate|e<j>.up|e<j>.down|shared.gate|
  * shared.up|shared.down|shared.sg" (bf16 [out, in]; the engine widens them for TGIS_DTYPE_F32). */
 int tgis_engine_create_spec(const tgis_config* cfg, const tgis_model_spec* spec, tgis_engine** out);
+/* cfg->arch == TGIS_ARCH_FALERAX; parameter names: "embed", "final.norm", "l<i>.norm1|norm2", "l<i>.mlp.gate|up|down",
+ * TGIS_MIXER_PARALLEL "l<i>.mix.left.q|k|v|g|o|q.norm|k.norm|out", "l<i>.mix.right.q|k|v|g|o|norm|i|i.b|f|f.b|out";
+ * TGIS_MIXER_SELECTIVE_SCAN "l<i>.mix.in|conv|conv.b|x|dt|dt.b|A_log|D|o"; TGIS_MIXER_WKV "l<i>.mix.mu.r|mu.k|mu.v|mu.g|mu.w|
+ * r|k|v|g|w1|w2|w0|u|norm|o". */
 /* name: HF Llama parameter name ("model.layers.3.self_attn.q_proj.weight", "lm_head.weight", ...) or
  * "tgis.rope_cos_sin" ([max_model_len,128] bf16 = cos|sin); arch OPT: HF OPT parameter names
  * ("model.decoder.layers.3.self_attn.q_proj.bias", "model.decoder.embed_positions.weight" with >= max_model_len + 2 rows,

@@ -705,11 +705,30 @@ __global__ void __launch_bounds__(NORM_THREADS) resid_tail_kernel(ResidTail a, i
   const int t = blockIdx.x;
   const size_t base = (size_t)t * hidden;
   float ss = 0.f;
+  float rs_a = 1.f, rs_b = 1.f;
+  if (a.y_pair != nullptr) {   // two mixers side by side: each output is normed by itself first
+    float sa = 0.f, sb = 0.f;
+    for (int i = threadIdx.x * VEC; i < hidden; i += NORM_THREADS * VEC) {
+      const FV<VEC> ya = ld_fv<VEC>(a.y_main + base + i), yb = ld_fv<VEC>(a.y_pair + base + i);
+#pragma unroll
+      for (int e = 0; e < VEC; ++e) {
+        sa = fmaf(ya.v[e], ya.v[e], sa);
+        sb = fmaf(yb.v[e], yb.v[e], sb);
+      }
+    }
+    rs_a = 1.f / sqrtf(block_sum<NORM_THREADS>(sa, red) / (float)hidden + a.eps);
+    rs_b = 1.f / sqrtf(block_sum<NORM_THREADS>(sb, red) / (float)hidden + a.eps);
+  }
   for (int i = threadIdx.x * VEC; i < hidden; i += NORM_THREADS * VEC) {
     FV<VEC> y;
 #pragma unroll
     for (int e = 0; e < VEC; ++e) y.v[e] = 0.f;
-    if (a.y_main != nullptr) {
+    if (a.y_pair != nullptr) {
+      const FV<VEC> ya = ld_fv<VEC>(a.y_main + base + i), yb = ld_fv<VEC>(a.y_pair + base + i);
+      const FV<VEC> wa = ld_fv<VEC>(a.w_main + i), wb = ld_fv<VEC>(a.w_pair + i);
+#pragma unroll
+      for (int e = 0; e < VEC; ++e) y.v[e] = 0.5f * (ya.v[e] * rs_a * wa.v[e] + yb.v[e] * rs_b * wb.v[e]);
+    } else if (a.y_main != nullptr) {
       y = ld_fv<VEC>(a.y_main + base + i);
     } else {
       if (a.y_rows != nullptr)
@@ -743,7 +762,13 @@ __global__ void __launch_bounds__(NORM_THREADS) resid_tail_kernel(ResidTail a, i
     st_fv<VEC>(a.resid + base + i, r);
     st_fv<VEC>(row_buf + i, r);
   }
-  if (a.w_pre == nullptr) return;
+  if (a.w_pre == nullptr) {
+    if (a.cast_out != 0 && a.out != nullptr) {
+      __syncthreads();
+      for (int i = threadIdx.x; i < hidden; i += NORM_THREADS) st_dt(a.out, a.out_dtype, base + i, row_buf[i]);
+    }
+    return;
+  }
   const float rs2 = 1.f / sqrtf(block_sum<NORM_THREADS>(ss2, red) / (float)hidden + a.eps);
   for (int i = threadIdx.x * VEC; i < hidden; i += NORM_THREADS * VEC) {
     const FV<VEC> r = ld_fv<VEC>(row_buf + i), w = ld_fv<VEC>(a.w_pre + i);
@@ -764,8 +789,9 @@ cudaError_t resid_tail_launch(const ResidTail& a, int T, int hidden, cudaStream_
   if (T <= 0) return cudaSuccess;
   if (a.w_post == nullptr || a.resid == nullptr || (size_t)hidden * 4 > 48 * 1024) return cudaErrorInvalidValue;
   auto al16 = [](const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; };
+  if (a.y_pair != nullptr && (a.y_main == nullptr || a.w_main == nullptr || a.w_pair == nullptr)) return cudaErrorInvalidValue;
   const bool vec = hidden % 4 == 0 && al16(a.y_main) && al16(a.y_rows) && al16(a.y_side) && al16(a.resid) && al16(a.w_post) &&
-                   al16(a.w_pre) && al16(a.out);
+                   al16(a.w_pre) && al16(a.out) && al16(a.y_pair) && al16(a.w_main) && al16(a.w_pair);
   if (vec) return launch_k(resid_tail_kernel<4>, dim3(T), dim3(NORM_THREADS), (size_t)hidden * sizeof(float), stream, a, hidden);
   return launch_k(resid_tail_kernel<1>, dim3(T), dim3(NORM_THREADS), (size_t)hidden * sizeof(float), stream, a, hidden);
 }

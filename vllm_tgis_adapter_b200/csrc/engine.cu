@@ -234,7 +234,7 @@ struct tgis_engine {
   std::set<std::string> opt_loaded;  // tensor names seen by load_weight_opt (completeness check at start)
   std::vector<LayerW> layers;
   CUtensorMap m_lm{};
-  // ---- layer-list architectures (TGIS_ARCH_PONENEX): per-layer geometry, weights, caches and the fp32-residual buffers
+  // ---- layer-list architectures (TGIS_ARCH_PONENEX, TGIS_ARCH_FALERAX): per-layer geometry, weights, caches and the fp32-residual buffers
   bool pnx_on = false;
   tgis_model_spec pnx_spec{};
   std::vector<tgis_layer_spec> pnx_layer_specs;
@@ -248,6 +248,24 @@ struct tgis_engine {
     void *w_router = nullptr, *w_gu_e = nullptr, *w_d_e = nullptr, *w_gu_s = nullptr, *w_d_s = nullptr;
     float* router_b = nullptr;
     int n_down() const { return sp.q_rank + sp.kv_rank + sp.rot_dim + sp.heads; }
+    // ---- mixers with state slots and the dense feed-forward (TGIS_ARCH_FALERAX)
+    void* w_in = nullptr;             // every projection that reads the mixer input, stacked ([in_cols, width], operand type)
+    int in_cols = 0;                  // ... rounded up to a multiple of 8 (zero rows)
+    // TGIS_MIXER_PARALLEL: columns of the stacked projection, the attention's paged caches, both sides' small weights
+    CapAttnGeom ca{};
+    int c_q = 0, c_k = 0, c_v = 0, c_g = 0, c_mq = 0, c_mk = 0, c_mv = 0, c_mg = 0, c_mi = 0, c_mf = 0;
+    void *k_cache = nullptr, *v_cache = nullptr;   // [num_blocks][KV_BLOCK][kv_heads * dim | vdim], operand type
+    void* w_o2 = nullptr;                          // the matrix memory's output projection
+    float *qk_norm = nullptr, *mm_norm = nullptr, *mm_bias = nullptr, *out_l = nullptr, *out_r = nullptr;
+    float *st_S = nullptr, *st_n = nullptr, *st_m = nullptr;   // per sequence slot: matrix, normaliser, running maximum
+    // TGIS_MIXER_SELECTIVE_SCAN
+    void *w_x = nullptr, *w_dt = nullptr;
+    float *conv_w = nullptr, *conv_b = nullptr, *dt_b = nullptr, *A_log = nullptr, *Dv = nullptr, *st_conv = nullptr;
+    // TGIS_MIXER_WKV (w_in: r | k | v | g, each reading its own mix)
+    void *w_w1 = nullptr, *w_w2 = nullptr;
+    float *mu = nullptr, *w0 = nullptr, *u = nullptr, *st_prev = nullptr;
+    // TGIS_MLP_DENSE_GELU: gate / up rows interleaved, down
+    void *w_gu = nullptr, *w_d = nullptr;
   };
   std::vector<PnxLayer> pnx_layers;
   std::vector<void*> pnx_allocs;                     // everything pnx_alloc handed out
@@ -258,6 +276,9 @@ struct tgis_engine {
   void *pnx_embed = nullptr, *pnx_head = nullptr, *pnx_hA = nullptr, *pnx_cq = nullptr, *pnx_oA = nullptr, *pnx_actS = nullptr,
        *pnx_actE = nullptr, *pnx_last = nullptr;
   void *pnx_q = nullptr, *pnx_olat = nullptr;  // operand type: they feed the per-head products
+  bool post_norm = false, tied_head = false;   // TGIS_STYLE_*
+  float *flx_f1 = nullptr, *flx_f2 = nullptr, *flx_f3 = nullptr;   // fp32 scratch of the recurrent mixers
+  void *flx_op2 = nullptr, *flx_mix = nullptr;                     // operand-type scratch: gated memory output, token-shift mixes
   float *pnx_final_norm = nullptr, *pnx_resid = nullptr, *pnx_y1 = nullptr, *pnx_gate = nullptr,
         *pnx_qabs = nullptr, *pnx_o = nullptr, *pnx_rl = nullptr, *pnx_mixw = nullptr, *pnx_sgate = nullptr,
         *pnx_yS = nullptr, *pnx_yE = nullptr;
@@ -464,7 +485,7 @@ struct tgis_engine {
     Fl = c.ffn / tp;
     Vl = c.vocab / tp;
     opt = c.arch == TGIS_ARCH_OPT;
-    pnx_on = c.arch == TGIS_ARCH_PONENEX;
+    pnx_on = c.arch == TGIS_ARCH_PONENEX || c.arch == TGIS_ARCH_FALERAX;  // the layer-list architectures
     if (pnx_on) logits_bf16 = false;  // fp32 logits straight from the accumulators
     model_head_dim = opt ? c.head_dim : HEAD_DIM;
     attn_scale = 1.0f / std::sqrt((float)model_head_dim);  // zero-padded head dims add nothing to q . k
@@ -638,7 +659,7 @@ struct tgis_engine {
     off_rows = place(sizeof(SampleRow) * (size_t)S_max);
     off_epoch = place(4 * sizeof(uint32_t));  // tensor parallelism: exchange epochs before this step ([0], [1]: per
                                                // parity) and the logits-gather epoch ([2])
-    off_ltiles = place(sizeof(LatentTile) * (size_t)(T_max + S_max));  // latent-attention query tiles (TGIS_ARCH_PONENEX)
+    off_ltiles = place(sizeof(LatentTile) * (size_t)(T_max + S_max));  // attention query tiles of the layer-list architectures
     off_bt = place(4 * (size_t)S_max * bt_stride);
     // decode work items follow the USED part of the block table (items_off(S)); room for the worst case
     place(sizeof(DecItem) * (1 + (size_t)S_max * max_splits_cap));
@@ -1133,7 +1154,7 @@ struct tgis_engine {
   }
 
   // ------------------------------------------------------------------------------------------------ layer-list models
-  // TGIS_ARCH_PONENEX.  Scheduler, sequence slots, block manager, step metadata, lm_head rows, sampler and CUDA-graph
+  // TGIS_ARCH_PONENEX / TGIS_ARCH_FALERAX.  Scheduler, sequence slots, block manager, step metadata, lm_head rows, sampler and CUDA-graph
   // replay are the engine's; what differs is the layer stack (pnx_forward) and the per-layer cache of latent rows, which
   // is paged with the same block ids as every other model's KV cache.
   template <class T>
@@ -1172,10 +1193,13 @@ struct tgis_engine {
     pnx_dt = pnx_spec.dtype == TGIS_DTYPE_F32 ? DT_F32 : DT_BF16;
     if (const char* e = getenv("TGIS_PNX_TC")) pnx_tc = atoi(e) != 0;
     if (const char* e = getenv("TGIS_DUMP_RESID")) pnx_dump_path = e;
+    post_norm = (pnx_spec.style & TGIS_STYLE_POST_NORM) != 0;
+    tied_head = (pnx_spec.style & TGIS_STYLE_TIED_HEAD) != 0;
     pnx_embed = pnx_alloc_dt(V * W);
-    pnx_head = pnx_alloc_dt(V * W);
+    pnx_head = tied_head ? pnx_embed : pnx_alloc_dt(V * W);
     pnx_final_norm = pnx_alloc<float>(W);
-    pnx_expected_tensors = 3;
+    pnx_expected_tensors = tied_head ? 2 : 3;
+    size_t m_f1 = 1, m_f2 = 1, m_f3 = 1, m_mix = 1;
     size_t m_down = 1, m_qr = 1, m_q = 1, m_qabs = 1, m_olat = 1, m_ov = 1, m_heads = 1, m_E = 1, m_top = 1, m_ff = 1, m_ffs = 1;
     size_t cache_row_bytes = 0;
     pnx_tile_tokens = LATENT_PAIRS;
@@ -1184,6 +1208,80 @@ struct tgis_engine {
       PnxLayer& l = pnx_layers[i];
       const tgis_layer_spec& s = pnx_layer_specs[i];
       l.sp = s;
+      if (s.mlp == TGIS_MLP_DENSE_GELU) {
+        l.norm2 = pnx_alloc<float>(W);
+        l.w_gu = pnx_alloc_dt((size_t)2 * s.ff * W);
+        l.w_d = pnx_alloc_dt(W * s.ff);
+        pnx_expected_tensors += 4;  // norm2, mlp.gate, mlp.up, mlp.down
+        m_ffs = std::max<size_t>(m_ffs, s.ff);
+      }
+      if (s.mixer != TGIS_MIXER_LATENT_ATTENTION) {
+        l.norm1 = pnx_alloc<float>(W);
+        pnx_expected_tensors += 1;
+        const size_t slots = S_max;
+        if (s.mixer == TGIS_MIXER_PARALLEL) {
+          l.ca = CapAttnGeom{s.heads, s.kv_heads, s.dim, s.vdim, s.scale, s.softcap, s.qt_coef, s.qt_every};
+          const int H = s.heads, G = s.kv_heads, mH = s.mm_heads;
+          int col = 0;
+          auto colsz = [&](int n) { const int r = col; col += n; return r; };
+          l.c_q = colsz(H * s.dim); l.c_k = colsz(G * s.dim); l.c_v = colsz(G * s.vdim); l.c_g = colsz(H * s.vdim);
+          l.c_mq = colsz(mH * s.mm_dim); l.c_mk = colsz(mH * s.mm_dim); l.c_mv = colsz(mH * s.mm_vdim);
+          l.c_mg = colsz(mH * s.mm_vdim); l.c_mi = colsz(mH); l.c_mf = colsz(mH);
+          l.in_cols = (col + 7) / 8 * 8;
+          l.w_in = pnx_alloc_dt((size_t)l.in_cols * W, true);
+          l.w_o = pnx_alloc_dt(W * H * s.vdim);
+          l.w_o2 = pnx_alloc_dt(W * mH * s.mm_vdim);
+          l.qk_norm = pnx_alloc<float>((size_t)2 * s.dim);
+          l.mm_norm = pnx_alloc<float>((size_t)mH * s.mm_vdim);
+          l.mm_bias = pnx_alloc<float>((size_t)2 * mH);
+          l.out_l = pnx_alloc<float>(W);
+          l.out_r = pnx_alloc<float>(W);
+          l.st_S = pnx_alloc<float>(slots * mH * s.mm_dim * s.mm_vdim, true);
+          l.st_n = pnx_alloc<float>(slots * mH * s.mm_dim, true);
+          l.st_m = pnx_alloc<float>(slots * mH, true);
+          pnx_expected_tensors += 19;  // left.{q,k,v,g,o,q.norm,k.norm,out}, right.{q,k,v,g,o,norm,i,i.b,f,f.b,out}
+          m_q = std::max<size_t>(m_q, (size_t)H * s.dim);
+          m_ov = std::max<size_t>(m_ov, (size_t)H * s.vdim);
+          m_f1 = std::max<size_t>(m_f1, (size_t)mH * s.mm_vdim);
+          cache_row_bytes += (size_t)G * (s.dim + s.vdim) * dt_size(pnx_dt);
+          pnx_tile_tokens = std::min(pnx_tile_tokens, CAPATTN_TILE);
+        } else if (s.mixer == TGIS_MIXER_SELECTIVE_SCAN) {
+          const size_t I = s.inner, N = s.state, R = s.dt_rank;
+          l.in_cols = (int)(2 * I);
+          l.w_in = pnx_alloc_dt(2 * I * W);
+          l.w_x = pnx_alloc_dt((R + 2 * N) * I);
+          l.w_dt = pnx_alloc_dt(I * R);
+          l.w_o = pnx_alloc_dt(W * I);
+          l.conv_w = pnx_alloc<float>(I * s.conv);
+          l.conv_b = pnx_alloc<float>(I);
+          l.dt_b = pnx_alloc<float>(I);
+          l.A_log = pnx_alloc<float>(I * N);
+          l.Dv = pnx_alloc<float>(I);
+          l.st_S = pnx_alloc<float>(slots * I * N, true);
+          l.st_conv = pnx_alloc<float>(slots * std::max(s.conv - 1, 1) * I, true);
+          pnx_expected_tensors += 9;  // in, conv, conv.b, x, dt, dt.b, A_log, D, o
+          m_ov = std::max(m_ov, I);
+          m_f1 = std::max(m_f1, I); m_f2 = std::max(m_f2, R + 2 * N); m_f3 = std::max(m_f3, I);
+        } else {  // TGIS_MIXER_WKV
+          const size_t A_ = (size_t)s.heads * s.dim, R = s.decay_rank;
+          l.in_cols = (int)(4 * A_);
+          l.w_in = pnx_alloc_dt(4 * A_ * W);
+          l.w_w1 = pnx_alloc_dt(R * W);
+          l.w_w2 = pnx_alloc_dt(A_ * R);
+          l.w_o = pnx_alloc_dt(W * A_);
+          l.mu = pnx_alloc<float>(5 * W);
+          l.w0 = pnx_alloc<float>(A_);
+          l.u = pnx_alloc<float>(A_);
+          l.mm_norm = pnx_alloc<float>(A_);
+          l.st_S = pnx_alloc<float>(slots * A_ * s.dim, true);
+          l.st_prev = pnx_alloc<float>(slots * W, true);
+          pnx_expected_tensors += 15;  // mu.{r,k,v,g,w}, r, k, v, g, w1, w2, w0, u, norm, o
+          m_qr = std::max(m_qr, R);
+          m_f1 = std::max(m_f1, A_); m_f2 = std::max(m_f2, A_); m_mix = std::max(m_mix, 5 * W);
+        }
+        m_down = std::max<size_t>(m_down, l.in_cols);
+        continue;
+      }
       l.g = LatentGeom{s.heads, s.dim, s.rot_dim, s.vdim, s.kv_rank, s.q_rank, s.window, s.rot_dims, s.scale};
       const size_t hd = (size_t)s.dim + s.rot_dim, row = (size_t)s.kv_rank + s.rot_dim;
       l.w_down = pnx_alloc_dt((size_t)l.n_down() * W);
@@ -1243,6 +1341,11 @@ struct tgis_engine {
     pnx_actE = pnx_alloc_dt(T * m_top * m_ff, true);
     pnx_yE = pnx_alloc<float>(T * m_top * W);
     pnx_last = pnx_alloc_dt(std::max<size_t>(logit_rows_cap, T) * W, true);
+    flx_f1 = pnx_alloc<float>(T * m_f1);
+    flx_f2 = pnx_alloc<float>(T * m_f2);
+    flx_f3 = pnx_alloc<float>(T * m_f3);
+    flx_op2 = pnx_alloc_dt(T * m_f1, true);
+    flx_mix = pnx_alloc_dt(T * m_mix, true);
     if (pnx_dt == DT_BF16) {
       pnx_attn_ws_floats = (size_t)8 << 20;  // 32 MB
       pnx_attn_ws = pnx_alloc<float>(pnx_attn_ws_floats);
@@ -1258,7 +1361,13 @@ struct tgis_engine {
     size_t nb = std::min(kv_bytes / std::max<size_t>(bytes_per_block, 1), (size_t)S_max * bt_stride + 1);
     if (nb < 1) throw CudaError("cache too small for one block");
     num_blocks = (int)nb;
-    for (PnxLayer& l : pnx_layers) l.cache = pnx_alloc_dt(nb * KV_BLOCK * l.g.row(), true);  // finite everywhere
+    for (PnxLayer& l : pnx_layers) {  // finite everywhere
+      if (l.sp.mixer == TGIS_MIXER_LATENT_ATTENTION) l.cache = pnx_alloc_dt(nb * KV_BLOCK * l.g.row(), true);
+      if (l.sp.mixer == TGIS_MIXER_PARALLEL) {
+        l.k_cache = pnx_alloc_dt(nb * KV_BLOCK * l.ca.kv_heads * l.ca.dim, true);
+        l.v_cache = pnx_alloc_dt(nb * KV_BLOCK * l.ca.kv_heads * l.ca.vdim, true);
+      }
+    }
     free_blocks.resize(num_blocks);
     for (int i = 0; i < num_blocks; ++i) free_blocks[i] = num_blocks - 1 - i;
   }
@@ -1284,7 +1393,7 @@ struct tgis_engine {
     auto mat = [&](void* dst, int64_t r, int64_t cc) { return place(dst, pnx_dt, r, cc, cc, 1); };
     auto vec = [&](float* dst, int64_t len) { return place(dst, DT_F32, len, 1, 1, 1); };
     if (name == "embed") return mat(pnx_embed, V, W);
-    if (name == "head") return mat(pnx_head, V, W);
+    if (name == "head" && !tied_head) return mat(pnx_head, V, W);
     if (name == "final.norm") return vec(pnx_final_norm, W);
     if (name.size() < 3 || name[0] != 'l') return fail("unknown weight " + name);
     const size_t dot = name.find('.');
@@ -1294,8 +1403,67 @@ struct tgis_engine {
     PnxLayer& l = pnx_layers[li];
     const tgis_layer_spec& s = l.sp;
     const std::string sub = name.substr(dot + 1);
-    const int64_t hd = s.dim + s.rot_dim;
     if (sub == "norm1") return vec(l.norm1, W);
+    if (s.mlp == TGIS_MLP_DENSE_GELU) {
+      // gate / up rows interleave (row 2j = gate_j, row 2j + 1 = up_j): one product, the gated activation in its epilogue
+      if (sub == "norm2") return vec(l.norm2, W);
+      if (sub == "mlp.gate") return place(l.w_gu, pnx_dt, s.ff, W, 2 * W, 1);
+      if (sub == "mlp.up") return place(at(l.w_gu, (size_t)W), pnx_dt, s.ff, W, 2 * W, 1);
+      if (sub == "mlp.down") return mat(l.w_d, W, s.ff);
+    }
+    auto in_rows = [&](int col, int64_t r) { return mat(at(l.w_in, (size_t)col * W), r, W); };
+    if (s.mixer == TGIS_MIXER_PARALLEL) {
+      const int64_t H = s.heads, G = s.kv_heads, mH = s.mm_heads;
+      if (sub == "mix.left.q") return in_rows(l.c_q, H * s.dim);
+      if (sub == "mix.left.k") return in_rows(l.c_k, G * s.dim);
+      if (sub == "mix.left.v") return in_rows(l.c_v, G * s.vdim);
+      if (sub == "mix.left.g") return in_rows(l.c_g, H * s.vdim);
+      if (sub == "mix.left.o") return mat(l.w_o, W, H * s.vdim);
+      if (sub == "mix.left.q.norm") return vec(l.qk_norm, s.dim);
+      if (sub == "mix.left.k.norm") return vec(l.qk_norm + s.dim, s.dim);
+      if (sub == "mix.left.out") return vec(l.out_l, W);
+      if (sub == "mix.right.q") return in_rows(l.c_mq, mH * s.mm_dim);
+      if (sub == "mix.right.k") return in_rows(l.c_mk, mH * s.mm_dim);
+      if (sub == "mix.right.v") return in_rows(l.c_mv, mH * s.mm_vdim);
+      if (sub == "mix.right.g") return in_rows(l.c_mg, mH * s.mm_vdim);
+      if (sub == "mix.right.i") return in_rows(l.c_mi, mH);
+      if (sub == "mix.right.f") return in_rows(l.c_mf, mH);
+      if (sub == "mix.right.i.b") return vec(l.mm_bias, mH);
+      if (sub == "mix.right.f.b") return vec(l.mm_bias + mH, mH);
+      if (sub == "mix.right.o") return mat(l.w_o2, W, mH * s.mm_vdim);
+      if (sub == "mix.right.norm") return vec(l.mm_norm, mH * s.mm_vdim);
+      if (sub == "mix.right.out") return vec(l.out_r, W);
+      return fail("unknown layer weight " + name);
+    }
+    if (s.mixer == TGIS_MIXER_SELECTIVE_SCAN) {
+      const int64_t I = s.inner, N = s.state, R = s.dt_rank;
+      if (sub == "mix.in") return mat(l.w_in, 2 * I, W);
+      if (sub == "mix.conv") return place(l.conv_w, DT_F32, I, s.conv, s.conv, 1);
+      if (sub == "mix.conv.b") return vec(l.conv_b, I);
+      if (sub == "mix.x") return mat(l.w_x, R + 2 * N, I);
+      if (sub == "mix.dt") return mat(l.w_dt, I, R);
+      if (sub == "mix.dt.b") return vec(l.dt_b, I);
+      if (sub == "mix.A_log") return place(l.A_log, DT_F32, I, N, N, 1);
+      if (sub == "mix.D") return vec(l.Dv, I);
+      if (sub == "mix.o") return mat(l.w_o, W, I);
+      return fail("unknown layer weight " + name);
+    }
+    if (s.mixer == TGIS_MIXER_WKV) {
+      const int64_t A_ = (int64_t)s.heads * s.dim, R = s.decay_rank;
+      static const char* const kMix[5] = {"r", "k", "v", "g", "w"};
+      for (int j = 0; j < 5; ++j) {
+        if (sub == std::string("mix.mu.") + kMix[j]) return vec(l.mu + (size_t)j * W, W);
+        if (j < 4 && sub == std::string("mix.") + kMix[j]) return in_rows((int)(j * A_), A_);
+      }
+      if (sub == "mix.w1") return mat(l.w_w1, R, W);
+      if (sub == "mix.w2") return mat(l.w_w2, A_, R);
+      if (sub == "mix.w0") return vec(l.w0, A_);
+      if (sub == "mix.u") return vec(l.u, A_);
+      if (sub == "mix.norm") return vec(l.mm_norm, A_);
+      if (sub == "mix.o") return mat(l.w_o, W, A_);
+      return fail("unknown layer weight " + name);
+    }
+    const int64_t hd = s.dim + s.rot_dim;
     if (sub == "norm1b") return vec(l.norm1b, W);
     if (sub == "mix.dq") return mat(l.w_down, s.q_rank, W);
     if (sub == "mix.dkv") return mat(at(l.w_down, (size_t)s.q_rank * W), s.kv_rank + s.rot_dim, W);
@@ -1375,7 +1543,8 @@ struct tgis_engine {
                 int mode = GEMM_ANY_PLAIN, bool x_tma_ok = true) {
     if (pnx_tc && x_tma_ok && pnx_dt == DT_BF16 && x_dt == DT_BF16 && ldx == K && K % 64 == 0 && K >= 256 && N % 8 == 0 &&
         N >= 128 && !cfg.debug_gemm_ref) {
-      const int out_mode = mode == GEMM_ANY_SWIGLU && y_dt == DT_BF16 ? 2 : mode == GEMM_ANY_PLAIN ? (y_dt == DT_F32 ? 1 : 0) : -1;
+      const int out_mode = mode == GEMM_ANY_SWIGLU && y_dt == DT_BF16 ? 2 : mode == GEMM_ANY_GEGLU && y_dt == DT_BF16 ? 3
+                           : mode == GEMM_ANY_PLAIN ? (y_dt == DT_F32 ? 1 : 0) : -1;
       if (out_mode >= 0 && pnx_gemm_tc(X, Wt, Y, ldy, T, N, K, out_mode)) return;
     }
     GemmAny a{};
@@ -1387,8 +1556,117 @@ struct tgis_engine {
     ++n_launches;
   }
 
+  void pnx_dump_resid(int T) {
+    if (pnx_dump_path.empty() || capturing) return;
+    CK(cudaStreamSynchronize(stream));
+    std::vector<float> hbuf((size_t)T * cfg.hidden);
+    CK(cudaMemcpy(hbuf.data(), pnx_resid, hbuf.size() * sizeof(float), cudaMemcpyDeviceToHost));
+    if (FILE* f = fopen(pnx_dump_path.c_str(), "ab")) {
+      fwrite(hbuf.data(), sizeof(float), hbuf.size(), f);
+      fclose(f);
+    }
+  }
+
+  // One layer of a post-norm stack (TGIS_STYLE_POST_NORM): x += rmsnorm(mixer(x)) * norm1, x += rmsnorm(ff(x)) * norm2.
+  // pnx_hA holds the stream in the operand type on entry and on exit (after the last layer: the final norm's output).
+  // T tokens of S sequences, any mix of whole prompts, portions and single tokens.
+  void stream_layer(int li, int T, int S) {
+    PnxLayer& l = pnx_layers[li];
+    const tgis_layer_spec& s = l.sp;
+    const int W = cfg.hidden, A = pnx_dt;
+    const float eps = pnx_spec.norm_eps;
+    const int32_t* d_pos = ds<int32_t>(off_pos);
+    const int32_t* d_slot = ds<int32_t>(off_slotmap);
+    const int32_t* d_tokslot = ds<int32_t>(off_tokslot);
+    const AttnSeq* d_seqs = ds<AttnSeq>(off_seqs);
+    const bool has_ff = s.mlp == TGIS_MLP_DENSE_GELU;
+    const bool last = li + 1 == (int)pnx_layers.size();
+    ResidTail rt{};
+    rt.resid = pnx_resid; rt.out = pnx_hA; rt.out_dtype = A; rt.mult = 1.f; rt.w_off = 0.f; rt.eps = eps;
+    rt.w_post = l.norm1;
+    rt.w_pre = (last && !has_ff) ? pnx_final_norm : nullptr;
+    rt.cast_out = 1;
+    if (s.mixer == TGIS_MIXER_PARALLEL) {
+      const int H = s.heads, mH = s.mm_heads, ld = l.in_cols;
+      // every projection of both sides in one product: [q | k | v | gate | q' | k' | v' | gate' | i | f]
+      pnx_gemm(pnx_hA, A, W, l.w_in, pnx_y1, DT_F32, ld, T, ld, W);
+      CK(capattn_prep_launch(pnx_y1, ld, l.c_q, l.c_k, l.c_v, l.ca, l.qk_norm, l.qk_norm + s.dim, eps, d_pos, d_slot, pnx_q,
+                             l.k_cache, l.v_cache, A, T, stream));
+      CK(capattn_launch(pnx_q, l.k_cache, l.v_cache, A, d_seqs, ds<LatentTile>(off_ltiles), step_n_ltiles, ds<int32_t>(off_bt),
+                        bt_stride, pnx_y1 + l.c_g, ld, pnx_oA, A, l.ca, stream));
+      pnx_gemm(pnx_oA, A, H * s.vdim, l.w_o, pnx_o, DT_F32, W, T, W, H * s.vdim);
+      OuterScan os{};
+      os.mode = OUTER_SCAN_GATED;
+      os.q = pnx_y1 + l.c_mq; os.k = pnx_y1 + l.c_mk; os.v = pnx_y1 + l.c_mv; os.ldq = os.ldk = os.ldv = ld;
+      os.q_scale = 1.f / std::sqrt((float)s.mm_dim);
+      os.ig = pnx_y1 + l.c_mi; os.fg = pnx_y1 + l.c_mf; os.ldg = ld; os.ig_b = l.mm_bias; os.fg_b = l.mm_bias + mH;
+      os.gate_cap = s.gate_cap;
+      os.S = l.st_S; os.n = l.st_n; os.m = l.st_m;
+      os.out = flx_f1; os.ldo = mH * s.mm_vdim;
+      os.heads = mH; os.dim = s.mm_dim; os.vdim = s.mm_vdim;
+      CK(outer_scan_launch(os, d_seqs, S, d_tokslot, stream));
+      CK(head_norm_gate_launch(flx_f1, mH * s.mm_vdim, mH, s.mm_vdim, l.mm_norm, pnx_y1 + l.c_mg, ld, /*sigmoid*/ 0, eps, flx_op2,
+                               A, T, stream));
+      n_launches += 4;
+      pnx_gemm(flx_op2, A, mH * s.mm_vdim, l.w_o2, pnx_yS, DT_F32, W, T, W, mH * s.mm_vdim);
+      rt.y_main = pnx_o; rt.y_pair = pnx_yS; rt.w_main = l.out_l; rt.w_pair = l.out_r;
+    } else if (s.mixer == TGIS_MIXER_SELECTIVE_SCAN) {
+      const int I = s.inner, N = s.state, R = s.dt_rank;
+      pnx_gemm(pnx_hA, A, W, l.w_in, pnx_y1, DT_F32, 2 * I, T, 2 * I, W);
+      CK(short_conv_silu_launch(pnx_y1, 2 * I, I, l.conv_w, l.conv_b, s.conv, d_pos, d_tokslot, l.st_conv, flx_f1,
+                                A == DT_F32 ? nullptr : pnx_oA, A, T, stream));
+      const void* xc = A == DT_F32 ? (const void*)flx_f1 : (const void*)pnx_oA;
+      pnx_gemm(xc, A, I, l.w_x, flx_f2, DT_F32, R + 2 * N, T, R + 2 * N, I);
+      pnx_gemm(flx_f2, DT_F32, R + 2 * N, l.w_dt, flx_f3, DT_F32, I, T, I, R);
+      SelScan sc{};
+      sc.x = flx_f1; sc.xz = pnx_y1; sc.ld_xz = 2 * I; sc.proj = flx_f2; sc.ld_proj = R + 2 * N; sc.dt_rank = R;
+      sc.dt_raw = flx_f3; sc.dt_b = l.dt_b; sc.A_log = l.A_log; sc.D = l.Dv; sc.S = l.st_S; sc.conv_state = l.st_conv;
+      sc.out = flx_op2; sc.out_dtype = A; sc.inner = I; sc.state = N; sc.taps = s.conv;
+      CK(selective_scan_launch(sc, d_seqs, S, d_tokslot, stream));
+      n_launches += 2;
+      pnx_gemm(flx_op2, A, I, l.w_o, pnx_o, DT_F32, W, T, W, I);
+      rt.y_main = pnx_o;
+    } else {  // TGIS_MIXER_WKV
+      const int H = s.heads, D = s.dim, Ad = H * D, R = s.decay_rank;
+      const long long bs = (long long)pnx_rows_alloc * W;   // one mix buffer
+      auto mix = [&](int j) { return reinterpret_cast<uint8_t*>(flx_mix) + (size_t)j * bs * dt_size(A); };
+      CK(token_shift_mix_launch(pnx_resid, W, l.mu, 5, d_pos, d_tokslot, l.st_prev, flx_mix, A, bs, T, stream));
+      for (int j = 0; j < 4; ++j)  // r | k | v | gate logits, each from its own mix
+        pnx_gemm(mix(j), A, W, reinterpret_cast<uint8_t*>(l.w_in) + (size_t)j * Ad * W * dt_size(A), pnx_y1 + (size_t)j * Ad, DT_F32,
+                 4 * Ad, T, Ad, W);
+      pnx_gemm(mix(4), A, W, l.w_w1, pnx_cq, A, R, T, R, W, GEMM_ANY_TANH);
+      pnx_gemm(pnx_cq, A, R, l.w_w2, flx_f2, DT_F32, Ad, T, Ad, R);
+      OuterScan os{};
+      os.mode = OUTER_SCAN_DECAY;
+      os.q = pnx_y1; os.k = pnx_y1 + Ad; os.v = pnx_y1 + 2 * Ad; os.ldq = os.ldk = os.ldv = 4 * Ad;
+      os.q_scale = 1.f;
+      os.decay_raw = flx_f2; os.ldd = Ad; os.w0 = l.w0; os.u = l.u;
+      os.S = l.st_S;
+      os.out = flx_f1; os.ldo = Ad;
+      os.heads = H; os.dim = D; os.vdim = D;
+      os.x = pnx_resid; os.x_last = l.st_prev; os.width = W;
+      CK(outer_scan_launch(os, d_seqs, S, d_tokslot, stream));
+      CK(head_norm_gate_launch(flx_f1, Ad, H, D, l.mm_norm, pnx_y1 + 3 * Ad, 4 * Ad, /*silu*/ 1, eps, flx_op2, A, T, stream));
+      n_launches += 3;
+      pnx_gemm(flx_op2, A, Ad, l.w_o, pnx_o, DT_F32, W, T, W, Ad);
+      rt.y_main = pnx_o;
+    }
+    CK(resid_tail_launch(rt, T, W, stream));
+    ++n_launches;
+    if (has_ff) {
+      pnx_gemm(pnx_hA, A, W, l.w_gu, pnx_actS, A, s.ff, T, 2 * s.ff, W, GEMM_ANY_GEGLU);
+      pnx_gemm(pnx_actS, A, s.ff, l.w_d, pnx_o, DT_F32, W, T, W, s.ff);
+      ResidTail r2{};
+      r2.resid = pnx_resid; r2.out = pnx_hA; r2.out_dtype = A; r2.mult = 1.f; r2.w_off = 0.f; r2.eps = eps;
+      r2.y_main = pnx_o; r2.w_post = l.norm2; r2.w_pre = last ? pnx_final_norm : nullptr; r2.cast_out = 1;
+      CK(resid_tail_launch(r2, T, W, stream));
+      ++n_launches;
+    }
+    pnx_dump_resid(T);
+  }
+
   // embeddings + layer stack + final norm -> pnx_hA [T, hidden] (operand type), fp32 residual stream in pnx_resid
-  void pnx_forward(int T) {
+  void pnx_forward(int T, int S) {
     const int W = cfg.hidden, A = pnx_dt;
     const float eps = pnx_spec.norm_eps, mult = pnx_spec.residual_mult;
     const int32_t* d_tok = ds<int32_t>(off_tok);
@@ -1398,10 +1676,15 @@ struct tgis_engine {
     const int32_t* d_bt = ds<int32_t>(off_bt);
     const LatentTile* d_tiles = ds<LatentTile>(off_ltiles);
     CK(embed_scale_f32_launch(d_tok, pnx_embed, A, pnx_spec.embed_scale, pnx_resid, T, W, cfg.vocab, stream));
-    CK(rmsnorm_f32_launch(pnx_resid, W, pnx_layers[0].norm1, 1.f, pnx_hA, A, W, T, W, eps, stream));
+    if (post_norm) CK(convert_f32_launch(pnx_resid, pnx_hA, A, (size_t)T * W, stream));
+    else CK(rmsnorm_f32_launch(pnx_resid, W, pnx_layers[0].norm1, 1.f, pnx_hA, A, W, T, W, eps, stream));
     n_launches += 2;
     const int L = (int)pnx_layers.size();
     for (int li = 0; li < L; ++li) {
+      if (post_norm) {
+        stream_layer(li, T, S);
+        continue;
+      }
       PnxLayer& l = pnx_layers[li];
       const tgis_layer_spec& s = l.sp;
       const LatentGeom& g = l.g;
@@ -1479,15 +1762,7 @@ struct tgis_engine {
         CK(resid_tail_launch(rt, T, W, stream));
         ++n_launches;
       }
-      if (!pnx_dump_path.empty() && !capturing) {
-        CK(cudaStreamSynchronize(stream));
-        std::vector<float> hbuf((size_t)T * W);
-        CK(cudaMemcpy(hbuf.data(), pnx_resid, hbuf.size() * sizeof(float), cudaMemcpyDeviceToHost));
-        if (FILE* f = fopen(pnx_dump_path.c_str(), "ab")) {
-          fwrite(hbuf.data(), sizeof(float), hbuf.size(), f);
-          fclose(f);
-        }
-      }
+      pnx_dump_resid(T);
     }
   }
 
@@ -1563,7 +1838,7 @@ struct tgis_engine {
     if (opt) {
       opt_layers(T, n_dec, n_tiles, max_dec_kv, S, R);  // embeddings + layer stack + final LayerNorm -> xn
     } else if (pnx_on) {
-      pnx_forward(T);  // embeddings + layer stack + final norm -> pnx_hA
+      pnx_forward(T, S);  // embeddings + layer stack + final norm -> pnx_hA
     } else {
       CK(embed_gather_launch(d_tok, embed, resid.p, T, H, V, stream));
       ++n_launches;
@@ -2504,7 +2779,7 @@ int tgis_abi_version(void) { return TGIS_ABI_VERSION; }
 int tgis_engine_create(const tgis_config* cfg, tgis_engine** out) {
   if (!cfg || !out) return fail("null argument");
   if (cfg->abi_version != TGIS_ABI_VERSION) return fail("ABI version mismatch");
-  if (cfg->arch == TGIS_ARCH_PONENEX) return fail("this architecture is described layer by layer: use tgis_engine_create_spec");
+  if (cfg->arch == TGIS_ARCH_PONENEX || cfg->arch == TGIS_ARCH_FALERAX) return fail("this architecture is described layer by layer: use tgis_engine_create_spec");
   if (cfg->arch != TGIS_ARCH_LLAMA && cfg->arch != TGIS_ARCH_OPT) return fail("unknown arch");
   if (cfg->arch == TGIS_ARCH_OPT) {
     if (cfg->head_dim != 64 && cfg->head_dim != HEAD_DIM) return fail("OPT: head_dim must be 64 or 128");
@@ -2550,7 +2825,7 @@ int tgis_engine_create(const tgis_config* cfg, tgis_engine** out) {
 int tgis_engine_create_spec(const tgis_config* cfg, const tgis_model_spec* spec, tgis_engine** out) {
   if (!cfg || !spec || !out || !spec->layers) return fail("null argument");
   if (cfg->abi_version != TGIS_ABI_VERSION) return fail("ABI version mismatch");
-  if (cfg->arch != TGIS_ARCH_PONENEX) return fail("tgis_engine_create_spec: arch must be TGIS_ARCH_PONENEX");
+  if (cfg->arch != TGIS_ARCH_PONENEX && cfg->arch != TGIS_ARCH_FALERAX) return fail("tgis_engine_create_spec: arch must be a layer-list architecture");
   if (spec->n_layers < 1 || spec->n_layers > 4096) return fail("bad n_layers");
   if (spec->dtype != TGIS_DTYPE_BF16 && spec->dtype != TGIS_DTYPE_F32) return fail("dtype must be bf16 or fp32");
   if (cfg->hidden < 1 || cfg->hidden > 12288 || cfg->vocab < 1) return fail("bad hidden / vocab");
@@ -2560,7 +2835,27 @@ int tgis_engine_create_spec(const tgis_config* cfg, const tgis_model_spec* spec,
   for (int i = 0; i < spec->n_layers; ++i) {
     const tgis_layer_spec& s = spec->layers[i];
     const std::string at = " (layer " + std::to_string(i) + ")";
-    if (s.mixer != TGIS_MIXER_LATENT_ATTENTION) return fail("unknown mixer type" + at);
+    const bool post = (spec->style & TGIS_STYLE_POST_NORM) != 0;
+    if (post != (s.mixer != TGIS_MIXER_LATENT_ATTENTION)) return fail("this mixer does not run in this norm style" + at);
+    if (post) {
+      if (s.mlp != TGIS_MLP_NONE && s.mlp != TGIS_MLP_DENSE_GELU) return fail("unknown feed-forward kind" + at);
+      if (s.mlp == TGIS_MLP_DENSE_GELU && s.ff < 1) return fail("bad feed-forward width" + at);
+      if (s.mixer == TGIS_MIXER_PARALLEL) {
+        if (s.heads < 1 || s.kv_heads < 1 || s.heads % s.kv_heads != 0 || s.dim < 1 || s.vdim < 1 || s.vdim > CAPATTN_MAX_VDIM ||
+            s.dim > 512)
+          return fail("bad attention sizes" + at);
+        if (s.mm_heads < 1 || s.mm_dim < 1 || s.mm_dim > OUTER_SCAN_MAX_DIM || s.mm_vdim < 1 || !(s.gate_cap > 0.f))
+          return fail("bad matrix-memory sizes" + at);
+      } else if (s.mixer == TGIS_MIXER_SELECTIVE_SCAN) {
+        if (s.inner < 1 || s.state < 1 || s.state > SELSCAN_MAX_STATE || s.dt_rank < 1 || s.conv < 1 || s.conv > 64)
+          return fail("bad selective-scan sizes" + at);
+      } else if (s.mixer == TGIS_MIXER_WKV) {
+        if (s.heads < 1 || s.dim < 1 || s.dim > OUTER_SCAN_MAX_DIM || s.decay_rank < 1) return fail("bad wkv sizes" + at);
+      } else {
+        return fail("unknown mixer type" + at);
+      }
+      continue;
+    }
     if (s.heads < 1 || s.dim < 1 || s.rot_dim < 0 || s.vdim < 1 || s.kv_rank < 1 || s.q_rank < 1) return fail("bad mixer sizes" + at);
     if (s.kv_rank > 512) return fail("kv_rank > 512 unsupported" + at);
     if (s.rot_dims < 0 || s.rot_dims > s.rot_dim || (s.rot_dims & 1)) return fail("rot.dims must be even and <= rot_dim" + at);

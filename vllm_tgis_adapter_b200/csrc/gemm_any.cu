@@ -5,7 +5,7 @@
 //   batched  blockIdx.z walks equal problems whose operands lie a fixed stride apart (one problem per attention head),
 //   grouped  the rows are cut into segments (seg_off, on the device) and segment g multiplies with weight matrix g
 //            (one segment per expert of a mixture-of-experts layer); rows of X may be gathered through an index list,
-// and three epilogues (plain store, SwiGLU over interleaved gate/up rows, per-(row, batch) scale).
+// and five epilogues (plain store, SwiGLU or GeGLU over interleaved gate/up rows, per-(row, batch) scale, tanh).
 //
 // Every output element is the sum over k = 0 .. K-1 in ascending order inside one thread, so a row's result depends
 // neither on the other rows of the launch nor on where in a segment it landed.
@@ -38,6 +38,11 @@ template <>
 __device__ __forceinline__ float ld_as_float<__nv_bfloat16>(const __nv_bfloat16* p) { return __bfloat162float(*p); }
 __device__ __forceinline__ void st_from_float(float* p, float v) { *p = v; }
 __device__ __forceinline__ void st_from_float(__nv_bfloat16* p, float v) { *p = __float2bfloat16_rn(v); }
+// act(gate) * up: silu (GEMM_ANY_SWIGLU) or the tanh form of gelu (GEMM_ANY_GEGLU)
+__device__ __forceinline__ float glu_pair(int mode, float g, float u) {
+  if (mode == GEMM_ANY_SWIGLU) return g / (1.f + expf(-g)) * u;
+  return 0.5f * g * (1.f + tanhf(0.7978845608028654f * (g + 0.044715f * g * g * g))) * u;
+}
 
 template <class XT, class WT, class OT, int TM>
 __global__ void __launch_bounds__(ANY_THREADS) gemm_any_kernel(GemmAny a) {
@@ -123,20 +128,17 @@ __global__ void __launch_bounds__(ANY_THREADS) gemm_any_kernel(GemmAny a) {
     const int dst = row_dst[ty * TM + i];
     if (dst < 0) continue;
     const int n = n0 + tx * 4;
-    if (a.mode == GEMM_ANY_SWIGLU) {
-      // columns (2j, 2j + 1) = (gate_j, up_j): out[j] = silu(gate) * up
+    if (a.mode == GEMM_ANY_SWIGLU || a.mode == GEMM_ANY_GEGLU) {
+      // columns (2j, 2j + 1) = (gate_j, up_j): out[j] = act(gate) * up
 #pragma unroll
       for (int j = 0; j < 4; j += 2) {
-        if (n + j + 1 < a.N) {
-          const float g = acc[i][j], u = acc[i][j + 1];
-          st_from_float(Y + (size_t)dst * a.ldy + (n + j) / 2, g / (1.f + expf(-g)) * u);
-        }
+        if (n + j + 1 < a.N) st_from_float(Y + (size_t)dst * a.ldy + (n + j) / 2, glu_pair(a.mode, acc[i][j], acc[i][j + 1]));
       }
     } else {
       const float s = a.mode == GEMM_ANY_ROWSCALE ? a.row_scale[(size_t)dst * a.scale_ld + z] : 1.f;
 #pragma unroll
       for (int j = 0; j < 4; ++j)
-        if (n + j < a.N) st_from_float(Y + (size_t)dst * a.ldy + n + j, acc[i][j] * s);
+        if (n + j < a.N) st_from_float(Y + (size_t)dst * a.ldy + n + j, a.mode == GEMM_ANY_TANH ? tanhf(acc[i][j]) : acc[i][j] * s);
     }
   }
 }
@@ -282,8 +284,11 @@ __global__ void __launch_bounds__(ANY_THREADS) gemm_any_mma_kernel(GemmAny a) {
       for (int ni = 0; ni < 4; ++ni) {
         const int n = n0 + wn * 32 + ni * 8 + t2;
         const float v0 = acc[mi][ni][half * 2], v1 = acc[mi][ni][half * 2 + 1];
-        if (a.mode == GEMM_ANY_SWIGLU) {
-          if (n + 1 < a.N) st_from_float(Y + (size_t)dst * a.ldy + n / 2, v0 / (1.f + expf(-v0)) * v1);
+        if (a.mode == GEMM_ANY_SWIGLU || a.mode == GEMM_ANY_GEGLU) {
+          if (n + 1 < a.N) st_from_float(Y + (size_t)dst * a.ldy + n / 2, glu_pair(a.mode, v0, v1));
+        } else if (a.mode == GEMM_ANY_TANH) {
+          if (n < a.N) st_from_float(Y + (size_t)dst * a.ldy + n, tanhf(v0));
+          if (n + 1 < a.N) st_from_float(Y + (size_t)dst * a.ldy + n + 1, tanhf(v1));
         } else {
           if (n < a.N) st_from_float(Y + (size_t)dst * a.ldy + n, v0 * s);
           if (n + 1 < a.N) st_from_float(Y + (size_t)dst * a.ldy + n + 1, v1 * s);
@@ -390,7 +395,7 @@ cudaError_t launch_tm(const GemmAny& a, cudaStream_t stream) {
 
 cudaError_t gemm_any_launch(const GemmAny& a, cudaStream_t stream) {
   if (a.T <= 0 || a.N <= 0) return cudaSuccess;
-  if (a.K <= 0 || (a.mode == GEMM_ANY_SWIGLU && (a.N & 1))) return cudaErrorInvalidValue;
+  if (a.K <= 0 || ((a.mode == GEMM_ANY_SWIGLU || a.mode == GEMM_ANY_GEGLU) && (a.N & 1))) return cudaErrorInvalidValue;
   if (a.mode == GEMM_ANY_ROWSCALE && a.row_scale == nullptr) return cudaErrorInvalidValue;
   if (a.gather != nullptr && a.gather_div <= 0) return cudaErrorInvalidValue;
   using bf = __nv_bfloat16;

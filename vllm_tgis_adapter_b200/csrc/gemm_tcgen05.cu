@@ -169,6 +169,13 @@ __device__ __forceinline__ __nv_bfloat16 swiglu_bf16(float gate_acc, float up_ac
   const float sl = bf16_round(g / (1.0f + expf(-g)));
   return __float2bfloat16_rn(sl * u);
 }
+// The gated pair of out mode 2 (SwiGLU, above) or 3: tanh-form GELU on the gate, evaluated on the fp32 accumulators and
+// rounded once
+__device__ __forceinline__ __nv_bfloat16 glu_bf16(int out_mode, float gate_acc, float up_acc) {
+  if (out_mode == 2) return swiglu_bf16(gate_acc, up_acc);
+  const float g = gate_acc;
+  return __float2bfloat16_rn(0.5f * g * (1.f + tanhf(0.7978845608028654f * (g + 0.044715f * g * g * g))) * up_acc);
+}
 
 // Fused RoPE + KV-cache scatter of the qkv projection's final epilogue (tile = one 128-dim head; arithmetic and rounding
 // points of rope_kvwrite_kernel).  Called by a full warp with a warp-uniform (head, t): this thread holds the fp32 sums of
@@ -559,14 +566,14 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap wmap, const __grid_
           tmem_ld_32x32b_x16(taddr + c0, r);
           tmem_ld_wait();
           if (!partial) {
-            if (out_f32 == 2) {
-              // fused SwiGLU: weight rows are interleaved (2j = gate_j, 2j+1 = up_j) so the pair sits in adjacent
+            if (out_f32 >= 2) {
+              // fused SwiGLU / GeGLU: weight rows are interleaved (2j = gate_j, 2j+1 = up_j) so the pair sits in adjacent
               // lanes; even lanes produce act[t, n/2]
 #pragma unroll
               for (int j = 0; j < 16; ++j) {
                 const float other = __shfl_xor_sync(0xffffffffu, __uint_as_float(r[j]), 1);
                 if ((row & 1) == 0 && n < N && c0 + j < t_valid)
-                  Y[(size_t)(t_base + c0 + j) * ldy + (n >> 1)] = swiglu_bf16(__uint_as_float(r[j]), other);
+                  Y[(size_t)(t_base + c0 + j) * ldy + (n >> 1)] = glu_bf16(out_f32, __uint_as_float(r[j]), other);
               }
             } else if (n < N) {
 #pragma unroll
@@ -680,10 +687,10 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap wmap, const __grid_
                 const float av[4] = {acc[j].x, acc[j].y, acc[j].z, acc[j].w};
                 if (rope.positions != nullptr) {  // qkv projection: RoPE + KV scatter (warp-uniform t and tile)
                   qkv_rope_store(rope, nt, t_base + t, r4, av, Y + o);
-                } else if (out_f32 == 2) {  // fused SwiGLU: rows (n4, n4+1) and (n4+2, n4+3) are (gate, up) pairs
+                } else if (out_f32 >= 2) {  // fused SwiGLU / GeGLU: rows (n4, n4+1) and (n4+2, n4+3) are (gate, up) pairs
                   __nv_bfloat16* yo = Y + (size_t)(t_base + t) * ldy + (n4 >> 1);
-                  if (n4 + 1 < N) yo[0] = swiglu_bf16(av[0], av[1]);
-                  if (n4 + 3 < N) yo[1] = swiglu_bf16(av[2], av[3]);
+                  if (n4 + 1 < N) yo[0] = glu_bf16(out_f32, av[0], av[1]);
+                  if (n4 + 3 < N) yo[1] = glu_bf16(out_f32, av[2], av[3]);
                 } else if (n4 + 3 < N && (ldy & 3) == 0) {
                   if (out_f32 == 1) {
                     *reinterpret_cast<float4*>(Yf + o) = acc[j];
@@ -835,10 +842,10 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap wmap, const __grid_
               if (lane_id() == 0) norm.sumsq_out[(size_t)t * (N / GEMM_BN) + nt] = ssq;
             } else if (rope.positions != nullptr) {
               qkv_rope_store(rope, nt, t, r4, av, Y + o);
-            } else if (out_f32 == 2) {
+            } else if (out_f32 >= 2) {
               __nv_bfloat16* yo = Y + (size_t)t * ldy + (n4 >> 1);
-              if (n4 + 1 < N) yo[0] = swiglu_bf16(av[0], av[1]);
-              if (n4 + 3 < N) yo[1] = swiglu_bf16(av[2], av[3]);
+              if (n4 + 1 < N) yo[0] = glu_bf16(out_f32, av[0], av[1]);
+              if (n4 + 3 < N) yo[1] = glu_bf16(out_f32, av[2], av[3]);
             } else if (n4 + 3 < N && (ldy & 3) == 0) {
               if (out_f32 == 1) {
                 *reinterpret_cast<float4*>(Yf + o) = acc[j];

@@ -30,7 +30,8 @@ int gemm_grid_size(int T, int N, int K, int num_sms);
 int gemm_even_split(int T, int N, int K, int num_sms);  // every tile cut over this many consecutive CTAs, or 0
 GemmNext gemm_next_desc(int T_next, int N_next, int K_next, int num_sms, int kb_prefetch);
 // Y: bf16 [T, ldy] (out_f32 = 0), fp32 [T, ldy] (out_f32 = 1, lm_head logits), or out_f32 = 2: fused SwiGLU — W rows are
-// interleaved (gate_j, up_j) pairs and Y is bf16 [T, ldy >= N/2] = bf16(bf16(silu(gate)) * up)
+// interleaved (gate_j, up_j) pairs and Y is bf16 [T, ldy >= N/2] = bf16(bf16(silu(gate)) * up); out_f32 = 3: the same with
+// the tanh form of gelu on the gate, evaluated on the fp32 accumulators (GeGLU)
 // Optional fused epilogue of the qkv projection (cluster mode only, gemm_cluster_split() > 0): RoPE on the q / k heads
 // and scatter of k / v into the paged cache, replacing rope_kvwrite_kernel.  N must be (n_q + 2 n_kv) * 128.
 struct GemmRope {
@@ -238,6 +239,8 @@ inline size_t dt_size(int dt) { return dt == DT_BF16 ? 2 : 4; }
 constexpr int GEMM_ANY_PLAIN = 0;     // Y[row, n] = acc
 constexpr int GEMM_ANY_SWIGLU = 1;    // W rows interleaved (gate_j, up_j): Y[row, j] = silu(acc[2j]) * acc[2j + 1], N = 2 ff
 constexpr int GEMM_ANY_ROWSCALE = 2;  // Y[row, n] = acc * row_scale[row * scale_ld + batch index]
+constexpr int GEMM_ANY_GEGLU = 3;     // as SWIGLU with the tanh form of gelu on the gate
+constexpr int GEMM_ANY_TANH = 4;      // Y[row, n] = tanh(acc)
 struct GemmAny {
   const void* X; const void* W; void* Y;
   int x_dtype, w_dtype, y_dtype;   // DT_*
@@ -267,6 +270,9 @@ cudaError_t embed_scale_f32_launch(const int32_t* token_ids, const void* table, 
 //             = sum_k mix_w[t, k] * y_rows[inv[t * top + k]] + side_gate[t] * y_side[t]     (terms with null pointers drop out)
 //   resid[t] += mult * rmsnorm(y[t]) * (w_off + w_post)
 //   out[t]    = rmsnorm(resid[t]) * (w_off + w_pre)                      (w_pre != nullptr: the next sublayer's input)
+//             = (rmsnorm(y_main[t]) * w_main + rmsnorm(y_pair[t]) * w_pair) / 2             (y_pair != nullptr: two mixers
+//                                                                                            side by side, plain weights)
+//   cast_out != 0 (and w_pre == nullptr): out[t] = resid[t] in the operand type -- the next sublayer reads the stream itself
 struct ResidTail {
   const float* y_main;
   const float* y_rows; const int32_t* inv; const float* mix_w; int top;
@@ -274,6 +280,8 @@ struct ResidTail {
   const float* w_post; const float* w_pre;
   float* resid; void* out; int out_dtype;
   float mult, w_off, eps;
+  const float* y_pair; const float* w_main; const float* w_pair;
+  int cast_out;
 };
 cudaError_t resid_tail_launch(const ResidTail& a, int T, int hidden, cudaStream_t stream);
 // rows of any DT_* matrix: out[r, :] = x[rows[r], :]
@@ -320,6 +328,85 @@ cudaError_t latent_attn_launch(const float* q_abs, const void* cache, int dtype,
                                const LatentTile* tiles, int n_tiles, const int32_t* block_table, int bt_stride,
                                void* o_lat, int o_dtype, const LatentGeom& g, cudaStream_t stream, float* split_ws = nullptr,
                                size_t split_ws_floats = 0, int max_kv_len = 0, int num_sms = 148, int* n_launched = nullptr);
+
+// ---- attention_capped.cu: grouped-query attention with normed queries / keys and a soft cap on the scores ------------
+// No rotation: positions enter through the causal mask and a query temperature.  Per head: q <- rmsnorm(q) * w_q *
+// (1 + qt_coef * ln(floor((pos + 1) / qt_every) + 1)), k <- rmsnorm(k) * w_k (one weight of `dim` entries for all heads);
+// score = scale * q . k, then softcap * tanh(score / softcap) (softcap <= 0: none); softmax over the keys j <= i; query head h
+// reads key/value head h / (heads / kv_heads); the heads' outputs are multiplied by sigmoid(gate logits).
+struct CapAttnGeom {
+  int heads, kv_heads, dim, vdim;
+  float scale, softcap, qt_coef;
+  int qt_every;      // <= 0: no query temperature
+};
+constexpr int CAPATTN_TILE = 16;      // query tokens per CTA
+constexpr int CAPATTN_MAX_VDIM = 512; // value columns per head the kernel's accumulators cover
+// y fp32 [T, ldy] holds q at column q_off (heads * dim), k at k_off (kv_heads * dim), v at v_off (kv_heads * vdim):
+//   q_out DT_* [T, heads * dim]; cache rows K [num_blocks][KV_BLOCK][kv_heads * dim], V [..][kv_heads * vdim] at slot[t]
+cudaError_t capattn_prep_launch(const float* y, int ldy, int q_off, int k_off, int v_off, const CapAttnGeom& g,
+                                const float* w_q, const float* w_k, float eps, const int32_t* positions,
+                                const int32_t* slot_mapping, void* q_out, void* k_cache, void* v_cache, int dtype, int T,
+                                cudaStream_t stream);
+// out DT_* [T, heads * vdim] = softmax(.) V * sigmoid(gate[t * gate_ld + h * vdim + c])   (gate == nullptr: no gate)
+cudaError_t capattn_launch(const void* q, const void* k_cache, const void* v_cache, int dtype, const AttnSeq* seqs,
+                           const LatentTile* tiles, int n_tiles, const int32_t* block_table, int bt_stride,
+                           const float* gate, int gate_ld, void* out, int out_dtype, const CapAttnGeom& g,
+                           cudaStream_t stream);
+
+// ---- recurrent.cu: mixers that carry a state from token to token ----------------------------------------------------
+// Every sequence owns one state slot per layer (the engine's sequence slot).  A kernel reads the slot's state for the first
+// token of a portion unless that token's position is 0 (then the state is zero: a slot needs no clearing when it is handed
+// to a new sequence), walks the portion's tokens in order and leaves the state after the last one.  tok_slot[t] is the
+// slot of token t; consecutive tokens of one slot are consecutive positions of one sequence.
+// out[s][t] = x[t] + (prev(t) - x[t]) * mu[s]    s < n_mix; prev(t) = x[t - 1], the slot's saved row, or zeros at position 0
+cudaError_t token_shift_mix_launch(const float* x, int width, const float* mu, int n_mix, const int32_t* positions,
+                                   const int32_t* tok_slot, const float* prev_state, void* out, int out_dtype,
+                                   long long out_bs, int T, cudaStream_t stream);
+// out[t, c] = silu(b[c] + sum_j w[c, taps - 1 - j] * x(t - j, c)),  x = xz[:, :inner]; tokens before the portion come from
+// conv_state [slots][taps - 1][inner] (entry e: position first - (taps - 1) + e), positions < 0 are zeros
+cudaError_t short_conv_silu_launch(const float* xz, int ld, int inner, const float* w, const float* b, int taps,
+                                   const int32_t* positions, const int32_t* tok_slot, const float* conv_state,
+                                   float* out_f32, void* out_op, int out_dtype, int T, cudaStream_t stream);
+// Selective scan, one thread per channel:  dt = softplus(dt_raw + dt_b);  S[c, n] <- exp(dt A[c, n]) S[c, n] + dt x_c B_n;
+// y_c = S[c] . C + D_c x_c;  out = y * silu(z)   (A = -exp(A_log)).  Also moves the convolution's tail forward.
+struct SelScan {
+  const float* x;        // fp32 [T, inner] after convolution and silu
+  const float* xz; int ld_xz;   // in-projection [T, 2 inner]: the convolution's inputs and z
+  const float* proj; int ld_proj; int dt_rank;  // [dt (dt_rank) | B (state) | C (state)]
+  const float* dt_raw;   // fp32 [T, inner]
+  const float *dt_b, *A_log, *D;
+  float* S;              // [slots][inner][state]
+  float* conv_state;     // [slots][taps - 1][inner]
+  void* out; int out_dtype;
+  int inner, state, taps;
+};
+constexpr int SELSCAN_MAX_STATE = 128;
+cudaError_t selective_scan_launch(const SelScan& a, const AttnSeq* seqs, int n_seqs, const int32_t* tok_slot,
+                                  cudaStream_t stream);
+// Outer-product memories, per head a matrix S [dim, vdim] (fp32), the CTAs of one head split the value columns:
+//   OUTER_SCAN_DECAY:  o = (S + diag(u) k v^T)^T q;  S <- diag(w) S + k v^T,  w = exp(-exp(decay_raw + w0))
+//   OUTER_SCAN_GATED:  i = cap tanh((ig + b_i) / cap), f = logsigmoid(cap tanh((fg + b_f) / cap)), m' = max(f + m, i),
+//                      S <- e^(f + m - m') S + e^(i - m') k v^T, n likewise with k;  o = S^T q / (max(|n . q|, e^-m') + 1e-6)
+constexpr int OUTER_SCAN_DECAY = 0, OUTER_SCAN_GATED = 1;
+constexpr int OUTER_SCAN_MAX_DIM = 256;
+struct OuterScan {
+  int mode;
+  const float *q, *k, *v; int ldq, ldk, ldv;   // fp32 [T, heads * dim] / [T, heads * vdim]
+  float q_scale;
+  const float* decay_raw; int ldd; const float* w0; const float* u;   // DECAY: [T, heads * dim], [heads * dim], [heads * dim]
+  const float *ig, *fg; int ldg; const float *ig_b, *fg_b; float gate_cap;  // GATED: [T, heads], biases [heads]
+  float *S, *n, *m;      // state [slots][heads][dim][vdim], [slots][heads][dim], [slots][heads]
+  float* out; int ldo;   // fp32 [T, heads * vdim]
+  int heads, dim, vdim;
+  const float* x; float* x_last; int width;   // optional: x_last[slot] = x[last row of the portion] (the token shift's state)
+};
+cudaError_t outer_scan_launch(const OuterScan& a, const AttnSeq* seqs, int n_seqs, const int32_t* tok_slot,
+                              cudaStream_t stream);
+// out[t, h, :] = rmsnorm(o[t, h, :]) * w[h, :] * act(gate[t, h, :])    act: 0 sigmoid, 1 silu
+cudaError_t head_norm_gate_launch(const float* o, int ldo, int heads, int vdim, const float* w, const float* gate,
+                                  int ldg, int act, float eps, void* out, int out_dtype, int T, cudaStream_t stream);
+// out[i] = x[i] in the operand type
+cudaError_t convert_f32_launch(const float* x, void* out, int out_dtype, size_t n, cudaStream_t stream);
 
 // ---- moe.cu: top-k router and the bookkeeping of the grouped expert products ----------------------------------------
 // logits fp32 [T, ld] (columns [0, E): experts; column E, when side_gate != nullptr: the shared expert's gate logit):

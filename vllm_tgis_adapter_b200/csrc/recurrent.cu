@@ -1,0 +1,367 @@
+// Mixers that carry a state from token to token: the token shift and decayed outer-product memory of RWKV-style time
+// mixing, the gated matrix memory of xLSTM (mLSTM), the short convolution and selective scan of Mamba, and the per-head
+// norm + gate that follows the two memories.
+//
+// State lives in fp32, one slot per sequence and layer (the engine's sequence slot).  A kernel reads the slot's state
+// for the first token of a portion unless that token sits at position 0 -- then the state is zero, so a slot needs no
+// clearing when it passes to another sequence --, walks the portion's tokens in ascending order and leaves the state
+// behind the last one.  The arithmetic of a token therefore depends on the tokens before it only, never on how the
+// sequence was cut into steps, on the other sequences of the batch or on the slot.  Everything that enters a recurrence
+// (decays, gates, step sizes, normalisers) is evaluated in fp32 with expf / tanhf / log1pf, no fast-math forms.
+//
+// The scans are sequential over tokens and parallel over what is independent: channels (selective scan), heads and
+// value columns (outer-product memories).  A state update is done by the thread that owns the entry, in the launch that
+// is the LAST reader of the old state in its layer, so no launch reads a state another CTA of the same launch rewrites.
+#include <cstdint>
+
+#include "kernels.h"
+#include "launch.cuh"
+#include "ptx.cuh"
+
+namespace tgis {
+namespace {
+
+__device__ __forceinline__ void st_op(void* out, int dt, size_t i, float v) {
+  if (dt == DT_BF16) reinterpret_cast<__nv_bfloat16*>(out)[i] = __float2bfloat16_rn(v);
+  else reinterpret_cast<float*>(out)[i] = v;
+}
+__device__ __forceinline__ float silu_f(float z) { return z / (1.f + expf(-z)); }
+__device__ __forceinline__ float sigmoid_f(float z) { return 1.f / (1.f + expf(-z)); }
+__device__ __forceinline__ float softplus_f(float z) { return z > 20.f ? z : log1pf(expf(z)); }
+__device__ __forceinline__ float logsigmoid_f(float z) { return z >= 0.f ? -log1pf(expf(-z)) : z - log1pf(expf(z)); }
+__device__ __forceinline__ float warp_sum_f(float v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+  return v;
+}
+
+// ------------------------------------------------------------------------------------------------ token shift
+__global__ void __launch_bounds__(128)
+token_shift_mix_kernel(const float* __restrict__ x, int width, const float* __restrict__ mu, int n_mix,
+                       const int32_t* __restrict__ positions, const int32_t* __restrict__ tok_slot,
+                       const float* __restrict__ prev_state, void* __restrict__ out, int out_dtype, long long out_bs) {
+  griddep_launch();
+  griddep_wait();
+  const int t = blockIdx.x;
+  const int slot = tok_slot[t];
+  const float* prev = nullptr;   // nullptr: zeros
+  if (positions[t] > 0) prev = (t > 0 && tok_slot[t - 1] == slot) ? x + (size_t)(t - 1) * width : prev_state + (size_t)slot * width;
+  const float* xr = x + (size_t)t * width;
+  for (int i = threadIdx.x; i < width; i += 128) {
+    const float h = xr[i], d = (prev ? prev[i] : 0.f) - h;
+    for (int s = 0; s < n_mix; ++s) st_op(out, out_dtype, (size_t)s * out_bs + (size_t)t * width + i, fmaf(d, mu[(size_t)s * width + i], h));
+  }
+}
+
+// ------------------------------------------------------------------------------------------------ short convolution
+__global__ void __launch_bounds__(128)
+short_conv_silu_kernel(const float* __restrict__ xz, int ld, int inner, const float* __restrict__ w,
+                       const float* __restrict__ b, int taps, const int32_t* __restrict__ positions,
+                       const int32_t* __restrict__ tok_slot, const float* __restrict__ conv_state,
+                       float* __restrict__ out_f32, void* __restrict__ out_op, int out_dtype) {
+  griddep_launch();
+  griddep_wait();
+  const int t = blockIdx.x, c = blockIdx.y * 128 + threadIdx.x;
+  if (c >= inner) return;
+  const int slot = tok_slot[t], p = positions[t];
+  int nb = 0;  // predecessors of this token inside the batch (as far as the taps reach)
+  while (nb < taps - 1 && t - nb - 1 >= 0 && tok_slot[t - nb - 1] == slot) ++nb;
+  float acc = b[c];
+  for (int j = taps - 1; j >= 0; --j) {   // oldest input first
+    if (p - j < 0) continue;
+    const float v = j <= nb ? xz[(size_t)(t - j) * ld + c]
+                            : conv_state[((size_t)slot * (taps - 1) + (taps - 1 - j + nb)) * inner + c];
+    acc = fmaf(w[(size_t)c * taps + (taps - 1 - j)], v, acc);
+  }
+  const float y = silu_f(acc);
+  if (out_f32) out_f32[(size_t)t * inner + c] = y;
+  if (out_op) st_op(out_op, out_dtype, (size_t)t * inner + c, y);
+}
+
+// ------------------------------------------------------------------------------------------------ selective scan
+constexpr int SCAN_THREADS = 64, SCAN_CHUNK = 8;
+__global__ void __launch_bounds__(SCAN_THREADS)
+selective_scan_kernel(SelScan a, const AttnSeq* __restrict__ seqs, const int32_t* __restrict__ tok_slot) {
+  extern __shared__ float scan_smem[];
+  const int N = a.state;
+  float* Ss = scan_smem;                          // [N][SCAN_THREADS]
+  float* As = Ss + (size_t)N * SCAN_THREADS;      // [N][SCAN_THREADS]
+  float* BC = As + (size_t)N * SCAN_THREADS;      // [SCAN_CHUNK][2 N]
+  griddep_launch();
+  griddep_wait();
+  const AttnSeq sq = seqs[blockIdx.x];
+  const int tid = threadIdx.x, c = blockIdx.y * SCAN_THREADS + tid;
+  const bool live = c < a.inner;
+  const int slot = tok_slot[sq.q_start];
+  const int first = sq.kv_len - sq.q_len;   // position of the portion's first token
+  float* Sg = a.S + ((size_t)slot * a.inner + (live ? c : 0)) * N;
+  for (int n = 0; n < N; ++n) {
+    Ss[n * SCAN_THREADS + tid] = (live && first > 0) ? Sg[n] : 0.f;
+    As[n * SCAN_THREADS + tid] = live ? -expf(a.A_log[(size_t)c * N + n]) : 0.f;
+  }
+  const float dtb = live ? a.dt_b[c] : 0.f, Dc = live ? a.D[c] : 0.f;
+  for (int t0 = 0; t0 < sq.q_len; t0 += SCAN_CHUNK) {
+    const int nt = min(SCAN_CHUNK, sq.q_len - t0);
+    __syncthreads();
+    for (int i = tid; i < nt * 2 * N; i += SCAN_THREADS) {
+      const int tt = i / (2 * N), j = i % (2 * N);
+      BC[i] = a.proj[(size_t)(sq.q_start + t0 + tt) * a.ld_proj + a.dt_rank + j];
+    }
+    __syncthreads();
+    if (!live) continue;
+    for (int tt = 0; tt < nt; ++tt) {
+      const size_t row = (size_t)(sq.q_start + t0 + tt);
+      const float dt = softplus_f(a.dt_raw[row * a.inner + c] + dtb);
+      const float xv = a.x[row * a.inner + c];
+      const float dx = dt * xv;
+      const float* Bt = BC + (size_t)tt * 2 * N;
+      float y = 0.f;
+      for (int n = 0; n < N; ++n) {
+        const float s = fmaf(expf(dt * As[n * SCAN_THREADS + tid]), Ss[n * SCAN_THREADS + tid], dx * Bt[n]);
+        Ss[n * SCAN_THREADS + tid] = s;
+        y = fmaf(s, Bt[N + n], y);
+      }
+      y = fmaf(Dc, xv, y);
+      const float z = a.xz[row * a.ld_xz + a.inner + c];
+      st_op(a.out, a.out_dtype, row * a.inner + c, y * silu_f(z));
+    }
+  }
+  if (!live) return;
+  for (int n = 0; n < N; ++n) Sg[n] = Ss[n * SCAN_THREADS + tid];
+  // the convolution's tail: inputs of the last taps - 1 positions (entry e: position end - (taps - 1) + e)
+  const int K1 = a.taps - 1;
+  float* cs = a.conv_state + (size_t)slot * K1 * a.inner + c;
+  for (int e = 0; e < K1; ++e) {   // ascending: entry e + q_len is read before it could be rewritten
+    const int pp = sq.kv_len - K1 + e;
+    float v = 0.f;
+    if (pp >= first) v = a.xz[(size_t)(sq.q_start + pp - first) * a.ld_xz + c];
+    else if (pp >= 0) v = cs[(size_t)(e + sq.q_len) * a.inner];
+    cs[(size_t)e * a.inner] = v;
+  }
+}
+
+// ------------------------------------------------------------------------------------------------ outer-product memories
+// grid (sequences, heads, ceil(vdim / 32)); 256 threads = 8 row groups (warps) x 32 value columns (lanes).  Thread (g, c)
+// keeps rows g, g + 8, ... of column c in registers; a token's q / k / decay vectors are staged in shared memory one token
+// ahead; the row groups' partial sums meet in shared memory and warp 0 writes the token's outputs.
+constexpr int OS_GROUPS = 8, OS_COLS = 32, OS_THREADS = OS_GROUPS * OS_COLS;
+template <int RPT, int MODE>
+__global__ void __launch_bounds__(OS_THREADS)
+outer_scan_kernel(OuterScan a, const AttnSeq* __restrict__ seqs, const int32_t* __restrict__ tok_slot) {
+  __shared__ float vec[2][3][OUTER_SCAN_MAX_DIM];   // [buffer][q | k | w][dim]
+  __shared__ float nvec[OUTER_SCAN_MAX_DIM];        // GATED: the normaliser n
+  __shared__ float part[OS_GROUPS][OS_COLS + 1];
+  __shared__ float part_n[OS_GROUPS];
+  __shared__ float gates[2][2];                     // GATED: raw (i, f) of the staged token
+  griddep_launch();
+  griddep_wait();
+  const AttnSeq sq = seqs[blockIdx.x];
+  const int h = blockIdx.y, tid = threadIdx.x, g = tid >> 5, lane = tid & 31;
+  const int c = blockIdx.z * OS_COLS + lane;
+  const bool col_ok = c < a.vdim;
+  const int D = a.dim;
+  const int slot = tok_slot[sq.q_start];
+  const bool fresh = sq.kv_len - sq.q_len == 0;
+  float S[RPT];
+  float* Sg = a.S + (((size_t)slot * a.heads + h) * D) * a.vdim + (col_ok ? c : 0);
+#pragma unroll
+  for (int j = 0; j < RPT; ++j) {
+    const int i = g + j * OS_GROUPS;
+    S[j] = (!fresh && col_ok && i < D) ? Sg[(size_t)i * a.vdim] : 0.f;
+  }
+  float u_r[RPT];
+  float m_run = 0.f;
+  if (MODE == OUTER_SCAN_DECAY) {
+#pragma unroll
+    for (int j = 0; j < RPT; ++j) {
+      const int i = g + j * OS_GROUPS;
+      u_r[j] = i < D ? a.u[(size_t)h * D + i] : 0.f;
+    }
+  } else {
+    float* ng = a.n + ((size_t)slot * a.heads + h) * D;
+    for (int i = tid; i < D; i += OS_THREADS) nvec[i] = fresh ? 0.f : ng[i];
+    m_run = fresh ? 0.f : a.m[(size_t)slot * a.heads + h];
+  }
+  auto stage = [&](int tt, int buf) {   // token tt of the portion -> vec[buf]
+    const size_t row = (size_t)(sq.q_start + tt);
+    for (int i = tid; i < D; i += OS_THREADS) {
+      vec[buf][0][i] = a.q[row * a.ldq + (size_t)h * D + i] * a.q_scale;
+      vec[buf][1][i] = a.k[row * a.ldk + (size_t)h * D + i];
+      if (MODE == OUTER_SCAN_DECAY)
+        vec[buf][2][i] = expf(-expf(a.decay_raw[row * a.ldd + (size_t)h * D + i] + a.w0[(size_t)h * D + i]));
+    }
+    if (MODE == OUTER_SCAN_GATED && tid == 0) {
+      gates[buf][0] = a.ig[row * a.ldg + h] + a.ig_b[h];
+      gates[buf][1] = a.fg[row * a.ldg + h] + a.fg_b[h];
+    }
+  };
+  stage(0, 0);
+  for (int tt = 0; tt < sq.q_len; ++tt) {
+    const int buf = tt & 1;
+    __syncthreads();   // vec[buf] (and nvec) complete; part of the previous token consumed
+    const size_t row = (size_t)(sq.q_start + tt);
+    const float vc = col_ok ? a.v[row * a.ldv + (size_t)h * a.vdim + c] : 0.f;
+    float o = 0.f, nq = 0.f;
+    if (MODE == OUTER_SCAN_DECAY) {
+#pragma unroll
+      for (int j = 0; j < RPT; ++j) {
+        const int i = g + j * OS_GROUPS;
+        if (i < D) {
+          const float kv = vec[buf][1][i] * vc;
+          o = fmaf(vec[buf][0][i], fmaf(u_r[j], kv, S[j]), o);
+          S[j] = fmaf(vec[buf][2][i], S[j], kv);
+        }
+      }
+    } else {
+      const float ig = a.gate_cap * tanhf(gates[buf][0] / a.gate_cap);
+      const float fg = logsigmoid_f(a.gate_cap * tanhf(gates[buf][1] / a.gate_cap));
+      const float m_new = fmaxf(fg + m_run, ig);
+      const float da = expf(fg + m_run - m_new), db = expf(ig - m_new);
+      m_run = m_new;
+#pragma unroll
+      for (int j = 0; j < RPT; ++j) {
+        const int i = g + j * OS_GROUPS;
+        if (i < D) {
+          const float kk = vec[buf][1][i], qq = vec[buf][0][i];
+          S[j] = fmaf(da, S[j], db * kk * vc);
+          o = fmaf(qq, S[j], o);
+          const float nn = fmaf(da, nvec[i], db * kk);   // every lane of the row group computes the same value
+          nq = fmaf(nn, qq, nq);
+          __syncwarp();   // (i is uniform over the warp) every lane has read nvec[i] before lane 0 replaces it
+          if (lane == 0) nvec[i] = nn;
+        }
+      }
+      if (lane == 0) part_n[g] = nq;
+    }
+    part[g][lane] = o;
+    if (tt + 1 < sq.q_len) stage(tt + 1, buf ^ 1);
+    __syncthreads();
+    if (g == 0) {
+      float s = 0.f;
+#pragma unroll
+      for (int r = 0; r < OS_GROUPS; ++r) s += part[r][lane];
+      if (MODE == OUTER_SCAN_GATED) {
+        float d = 0.f;
+#pragma unroll
+        for (int r = 0; r < OS_GROUPS; ++r) d += part_n[r];
+        s = s / (fmaxf(fabsf(d), expf(-m_run)) + 1e-6f);
+      }
+      if (col_ok) a.out[row * a.ldo + (size_t)h * a.vdim + c] = s;
+    }
+  }
+  // ---- leave the state behind the portion's last token
+  if (col_ok) {
+#pragma unroll
+    for (int j = 0; j < RPT; ++j) {
+      const int i = g + j * OS_GROUPS;
+      if (i < D) Sg[(size_t)i * a.vdim] = S[j];
+    }
+  }
+  if (blockIdx.z == 0) {
+    if (MODE == OUTER_SCAN_GATED) {
+      __syncthreads();
+      float* ng = a.n + ((size_t)slot * a.heads + h) * D;
+      for (int i = tid; i < D; i += OS_THREADS) ng[i] = nvec[i];
+      if (tid == 0) a.m[(size_t)slot * a.heads + h] = m_run;
+    }
+    if (a.x_last != nullptr && h == 0) {
+      const float* src = a.x + (size_t)(sq.q_start + sq.q_len - 1) * a.width;
+      for (int i = tid; i < a.width; i += OS_THREADS) a.x_last[(size_t)slot * a.width + i] = src[i];
+    }
+  }
+}
+
+// ------------------------------------------------------------------------------------------------ head norm + gate
+__global__ void __launch_bounds__(128)
+head_norm_gate_kernel(const float* __restrict__ o, int ldo, int vdim, const float* __restrict__ w,
+                      const float* __restrict__ gate, int ldg, int act, float eps, void* __restrict__ out, int out_dtype,
+                      int out_ld) {
+  __shared__ float red[4];
+  griddep_launch();
+  griddep_wait();
+  const int t = blockIdx.x, h = blockIdx.y;
+  const float* orow = o + (size_t)t * ldo + (size_t)h * vdim;
+  float ss = 0.f;
+  for (int i = threadIdx.x; i < vdim; i += 128) ss = fmaf(orow[i], orow[i], ss);
+  ss = warp_sum_f(ss);
+  if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = ss;
+  __syncthreads();
+  const float rs = 1.f / sqrtf((red[0] + red[1] + red[2] + red[3]) / (float)vdim + eps);
+  for (int i = threadIdx.x; i < vdim; i += 128) {
+    const float gl = gate[(size_t)t * ldg + (size_t)h * vdim + i];
+    const float gv = act == 1 ? silu_f(gl) : sigmoid_f(gl);
+    st_op(out, out_dtype, (size_t)t * out_ld + (size_t)h * vdim + i, orow[i] * rs * w[(size_t)h * vdim + i] * gv);
+  }
+}
+
+__global__ void convert_f32_kernel(const float* __restrict__ x, void* __restrict__ out, int out_dtype, size_t n) {
+  griddep_launch();
+  griddep_wait();
+  for (size_t i = blockIdx.x * (size_t)blockDim.x + threadIdx.x; i < n; i += (size_t)gridDim.x * blockDim.x)
+    st_op(out, out_dtype, i, x[i]);
+}
+
+}  // namespace
+
+cudaError_t token_shift_mix_launch(const float* x, int width, const float* mu, int n_mix, const int32_t* positions,
+                                   const int32_t* tok_slot, const float* prev_state, void* out, int out_dtype,
+                                   long long out_bs, int T, cudaStream_t stream) {
+  if (T <= 0) return cudaSuccess;
+  return launch_k(token_shift_mix_kernel, dim3(T), dim3(128), 0, stream, x, width, mu, n_mix, positions, tok_slot, prev_state,
+                  out, out_dtype, out_bs);
+}
+
+cudaError_t short_conv_silu_launch(const float* xz, int ld, int inner, const float* w, const float* b, int taps,
+                                   const int32_t* positions, const int32_t* tok_slot, const float* conv_state,
+                                   float* out_f32, void* out_op, int out_dtype, int T, cudaStream_t stream) {
+  if (T <= 0) return cudaSuccess;
+  if (taps < 1) return cudaErrorInvalidValue;
+  return launch_k(short_conv_silu_kernel, dim3(T, (inner + 127) / 128), dim3(128), 0, stream, xz, ld, inner, w, b, taps,
+                  positions, tok_slot, conv_state, out_f32, out_op, out_dtype);
+}
+
+cudaError_t selective_scan_launch(const SelScan& a, const AttnSeq* seqs, int n_seqs, const int32_t* tok_slot,
+                                  cudaStream_t stream) {
+  if (n_seqs <= 0) return cudaSuccess;
+  if (a.state < 1 || a.state > SELSCAN_MAX_STATE || a.taps < 1) return cudaErrorInvalidValue;
+  const size_t smem = ((size_t)2 * a.state * SCAN_THREADS + (size_t)SCAN_CHUNK * 2 * a.state) * sizeof(float);
+  static size_t smem_set = 0;
+  if (smem > 48 * 1024 && smem > smem_set) {
+    const cudaError_t e = cudaFuncSetAttribute(selective_scan_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (e != cudaSuccess) return e;
+    smem_set = smem;
+  }
+  return launch_k(selective_scan_kernel, dim3(n_seqs, (a.inner + SCAN_THREADS - 1) / SCAN_THREADS), dim3(SCAN_THREADS), smem,
+                  stream, a, seqs, tok_slot);
+}
+
+template <int MODE>
+static cudaError_t outer_scan_mode(const OuterScan& a, const AttnSeq* seqs, int n_seqs, const int32_t* tok_slot,
+                                   cudaStream_t stream) {
+  const dim3 grid(n_seqs, a.heads, (a.vdim + OS_COLS - 1) / OS_COLS);
+  if (a.dim <= 8 * OS_GROUPS) return launch_k(outer_scan_kernel<8, MODE>, grid, dim3(OS_THREADS), 0, stream, a, seqs, tok_slot);
+  if (a.dim <= 16 * OS_GROUPS) return launch_k(outer_scan_kernel<16, MODE>, grid, dim3(OS_THREADS), 0, stream, a, seqs, tok_slot);
+  return launch_k(outer_scan_kernel<32, MODE>, grid, dim3(OS_THREADS), 0, stream, a, seqs, tok_slot);
+}
+cudaError_t outer_scan_launch(const OuterScan& a, const AttnSeq* seqs, int n_seqs, const int32_t* tok_slot,
+                              cudaStream_t stream) {
+  if (n_seqs <= 0) return cudaSuccess;
+  if (a.dim < 1 || a.dim > OUTER_SCAN_MAX_DIM || a.heads < 1 || a.heads > 65535 || a.vdim < 1) return cudaErrorInvalidValue;
+  return a.mode == OUTER_SCAN_GATED ? outer_scan_mode<OUTER_SCAN_GATED>(a, seqs, n_seqs, tok_slot, stream)
+                                    : outer_scan_mode<OUTER_SCAN_DECAY>(a, seqs, n_seqs, tok_slot, stream);
+}
+
+cudaError_t head_norm_gate_launch(const float* o, int ldo, int heads, int vdim, const float* w, const float* gate,
+                                  int ldg, int act, float eps, void* out, int out_dtype, int T, cudaStream_t stream) {
+  if (T <= 0) return cudaSuccess;
+  return launch_k(head_norm_gate_kernel, dim3(T, heads), dim3(128), 0, stream, o, ldo, vdim, w, gate, ldg, act, eps, out,
+                  out_dtype, heads * vdim);
+}
+
+cudaError_t convert_f32_launch(const float* x, void* out, int out_dtype, size_t n, cudaStream_t stream) {
+  if (n == 0) return cudaSuccess;
+  const int blocks = (int)std::min<size_t>((n + 255) / 256, 148 * 8);
+  return launch_k(convert_f32_kernel, dim3(blocks), dim3(256), 0, stream, x, out, out_dtype, n);
+}
+
+}  // namespace tgis

@@ -10,10 +10,11 @@ import ctypes as C
 import os
 from pathlib import Path
 
-ABI_VERSION = 8
-ARCH_LLAMA, ARCH_OPT, ARCH_PONENEX = 0, 1, 2
-MIXER_LATENT_ATTENTION = 1
-MLP_NONE, MLP_MOE = 0, 1
+ABI_VERSION = 9
+ARCH_LLAMA, ARCH_OPT, ARCH_PONENEX, ARCH_FALERAX = 0, 1, 2, 3
+MIXER_LATENT_ATTENTION, MIXER_PARALLEL, MIXER_SELECTIVE_SCAN, MIXER_WKV = 1, 2, 3, 4
+MLP_NONE, MLP_MOE, MLP_DENSE_GELU = 0, 1, 2
+STYLE_POST_NORM, STYLE_TIED_HEAD = 1, 2
 DTYPE_BF16, DTYPE_F32 = 0, 1
 MAX_REQUEST_ID = 96
 MAX_TOPN = 12
@@ -40,7 +41,11 @@ class TgisLayerSpec(C.Structure):
         ("mixer", C.c_int32), ("heads", C.c_int32), ("dim", C.c_int32), ("rot_dim", C.c_int32), ("vdim", C.c_int32),
         ("kv_rank", C.c_int32), ("q_rank", C.c_int32), ("window", C.c_int32), ("rot_dims", C.c_int32),
         ("rot_base", C.c_float), ("scale", C.c_float), ("mlp", C.c_int32), ("experts", C.c_int32), ("top", C.c_int32),
-        ("expert_ff", C.c_int32), ("shared_ff", C.c_int32), ("reserved", C.c_int32),
+        ("expert_ff", C.c_int32), ("shared_ff", C.c_int32), ("ff", C.c_int32),
+        ("kv_heads", C.c_int32), ("softcap", C.c_float), ("qt_coef", C.c_float), ("qt_every", C.c_int32),
+        ("mm_heads", C.c_int32), ("mm_dim", C.c_int32), ("mm_vdim", C.c_int32), ("gate_cap", C.c_float),
+        ("inner", C.c_int32), ("state", C.c_int32), ("dt_rank", C.c_int32), ("conv", C.c_int32),
+        ("decay_rank", C.c_int32), ("reserved", C.c_int32),
     ]
 
 
@@ -54,7 +59,7 @@ class TgisKLatentGeom(C.Structure):
 class TgisModelSpec(C.Structure):
     _fields_ = [
         ("n_layers", C.c_int32), ("dtype", C.c_int32), ("embed_scale", C.c_float), ("residual_mult", C.c_float),
-        ("norm_eps", C.c_float), ("reserved", C.c_int32), ("layers", C.POINTER(TgisLayerSpec)),
+        ("norm_eps", C.c_float), ("style", C.c_int32), ("layers", C.POINTER(TgisLayerSpec)),
     ]
 
 

@@ -12,7 +12,7 @@ import logging
 from pathlib import Path
 
 from .async_engine import AsyncTGISEngine
-from .core import PRESETS, ModelConfig, NativeEngine
+from .core import LAYER_LIST_ARCHS, PRESETS, ModelConfig, NativeEngine
 from .tokenizer import load_tokenizer
 
 logger = logging.getLogger("vllm_tgis_adapter.engine")
@@ -24,6 +24,10 @@ def model_config_from_hf(path: Path, max_model_len: int | None, dtype: str = "bf
         from .ponenex import model_config_from_json
 
         return model_config_from_json(cfg, max_model_len, dtype)
+    if cfg.get("architecture") == "Falerax":
+        from .falerax import checkpoint_shapes, model_config_from_json
+
+        return model_config_from_json(cfg, max_model_len, dtype, checkpoint_shapes(path))
     archs = cfg.get("architectures") or []
     if cfg.get("model_type") == "opt" or any("OPT" in a for a in archs):
         return _opt_model_config(cfg, max_model_len)
@@ -91,8 +95,11 @@ def load_synthetic_weights(eng: NativeEngine, mc: ModelConfig, seed: int, device
     def rnd(r, c):
         return (torch.randn(r, c, generator=gen, device=f"cuda:{device}", dtype=torch.float32) * 0.02).to(torch.bfloat16)
 
-    if mc.arch == "ponenex":
-        from .ponenex import iter_synthetic_weights
+    if mc.arch in LAYER_LIST_ARCHS:
+        if mc.arch == "ponenex":
+            from .ponenex import iter_synthetic_weights
+        else:
+            from .falerax import iter_synthetic_weights
 
         for name, t in iter_synthetic_weights(mc, seed, f"cuda:{device}"):
             eng.load_weight(name, t)
@@ -172,16 +179,18 @@ def _resolve_model(args):
     if path.is_dir():
         dtype = "float32" if getattr(args, "dtype", "auto") in ("float32", "fp32") else "bfloat16"
         mc = model_config_from_hf(path, args.max_model_len, dtype)
-        if dtype == "float32" and mc.arch != "ponenex":
+        if dtype == "float32" and mc.arch not in LAYER_LIST_ARCHS:
             raise ValueError(f"--dtype float32 is not available for the {mc.arch} architecture (bfloat16 only)")
         return mc, path
+    from .falerax import PRESETS as FALERAX_PRESETS
     from .ponenex import PRESETS as PONENEX_PRESETS
 
+    PONENEX_PRESETS = {**PONENEX_PRESETS, **FALERAX_PRESETS}   # the presets of the layer-list architectures
     if args.model in PRESETS or args.model in PONENEX_PRESETS:
         if not args.synthetic_weights:
             raise ValueError(f"--model {args.model} is a preset name: pass --synthetic-weights or a model directory")
         mc = dataclasses.replace((PRESETS.get(args.model) or PONENEX_PRESETS[args.model]))
-        if mc.arch == "ponenex" and getattr(args, "dtype", "auto") in ("float32", "fp32"):
+        if mc.arch in LAYER_LIST_ARCHS and getattr(args, "dtype", "auto") in ("float32", "fp32"):
             mc.dtype = "float32"
         if args.max_model_len:
             mc.max_model_len = args.max_model_len
@@ -198,7 +207,7 @@ def _make_native_engine(args, mc: ModelConfig, path, device: int, **tp_kw) -> Na
         load_safetensors_dir(eng, path)      # full tensors: a tensor-parallel engine keeps its rank's shard
     else:
         load_synthetic_weights(eng, mc, args.seed, device)
-    if mc.arch not in ("opt", "ponenex"):   # OPT: learned positions; Ponenex: per-layer tables built by the engine
+    if mc.arch == "llama":   # OPT: learned positions; Ponenex: per-layer tables built by the engine; Falerax: no rotation
         eng.load_weight("tgis.rope_cos_sin", rope_cos_sin(mc))
     return eng
 

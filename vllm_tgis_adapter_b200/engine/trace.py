@@ -35,13 +35,13 @@ def main(argv: list[str] | None = None) -> int:
     ap.add_argument("--device", type=int, default=0)
     args = ap.parse_args(argv)
 
-    from .core import KV_BLOCK_TOKENS, NativeEngine, cache_block_bytes
+    from .core import KV_BLOCK_TOKENS, LAYER_LIST_ARCHS, NativeEngine, cache_block_bytes
     from .loader import load_safetensors_dir, model_config_from_hf
 
     path = Path(args.model)
     pool_tokens = (args.max_tokens + ROUND_TO - 1) // ROUND_TO * ROUND_TO
     mc = model_config_from_hf(path, pool_tokens, args.dtype)
-    if args.dtype == "float32" and mc.arch != "ponenex":
+    if args.dtype == "float32" and mc.arch not in LAYER_LIST_ARCHS:
         print(f"the {mc.arch} architecture runs in bfloat16 only", file=sys.stderr)
         return 3
     eng = NativeEngine(mc, max_num_seqs=SEQ_SLOTS, max_batched_tokens=max(pool_tokens, 16),
