@@ -144,6 +144,45 @@ int tgis_k_moe_route(const float* logits, int32_t ld, const float* bias, int32_t
                      float* side_gate, int32_t T);
 int tgis_k_moe_align(const int32_t* ids, int32_t T, int32_t top, int32_t E, int32_t* seg_off, int32_t* order, int32_t* inv);
 
+/* ---- softcapped grouped-query attention (csrc/attention_capped.cu) ---- */
+typedef struct tgis_k_capattn_geom {
+  int32_t heads, kv_heads, dim, vdim;
+  float scale, softcap, qt_coef;
+  int32_t qt_every;
+} tgis_k_capattn_geom;
+/* y fp32 [T, ldy] with q / k / v at the given columns -> normed, temperature-scaled queries (dt) [T, heads * dim] and the
+ * cache rows K [blocks][32][kv_heads * dim], V [blocks][32][kv_heads * vdim] at slots[t] */
+int tgis_k_capattn_prep(const float* y, int32_t ldy, int32_t q_off, int32_t k_off, int32_t v_off, const tgis_k_capattn_geom* g,
+                        const float* w_q, const float* w_k, float eps, const int32_t* positions, const int32_t* slots,
+                        void* q_out, void* k_cache, void* v_cache, int32_t dt, int32_t T);
+/* seqs_host: n_seqs x {q_start, q_len, kv_len, block_row}; out (dt) [T, heads * vdim], times sigmoid(gate) when gate != NULL */
+int tgis_k_capattn(const void* q, const void* k_cache, const void* v_cache, int32_t dt, const int32_t* seqs_host, int32_t n_seqs,
+                   const int32_t* block_table_host, int32_t bt_rows, int32_t bt_stride, const float* gate, int32_t gate_ld,
+                   void* out, const tgis_k_capattn_geom* g);
+/* ---- mixers with per-slot state (csrc/recurrent.cu; tok_slot, positions: device [T]) ---- */
+int tgis_k_token_shift(const float* x, int32_t width, const float* mu, int32_t n_mix, const int32_t* positions,
+                       const int32_t* tok_slot, const float* prev_state, void* out, int32_t out_dt, int64_t out_bs, int32_t T);
+int tgis_k_short_conv(const float* xz, int32_t ld, int32_t inner, const float* w, const float* b, int32_t taps,
+                      const int32_t* positions, const int32_t* tok_slot, const float* conv_state, float* out_f32, void* out_op,
+                      int32_t out_dt, int32_t T);
+int tgis_k_selective_scan(const float* x, const float* xz, int32_t ld_xz, const float* proj, int32_t ld_proj, int32_t dt_rank,
+                          const float* dt_raw, const float* dt_b, const float* A_log, const float* D, float* S,
+                          float* conv_state, void* out, int32_t out_dt, int32_t inner, int32_t state, int32_t taps,
+                          const int32_t* seqs_host, int32_t n_seqs, const int32_t* tok_slot);
+/* mode 0: decayed memory with a current-token bonus (decay_raw, w0, u); mode 1: gated matrix memory (ig, fg, biases, cap, n, m) */
+int tgis_k_outer_scan(int32_t mode, const float* q, const float* k, const float* v, int32_t ldq, int32_t ldk, int32_t ldv,
+                      float q_scale, const float* decay_raw, int32_t ldd, const float* w0, const float* u, const float* ig,
+                      const float* fg, int32_t ldg, const float* ig_b, const float* fg_b, float gate_cap, float* S, float* n,
+                      float* m, float* out, int32_t ldo, int32_t heads, int32_t dim, int32_t vdim, const float* x, float* x_last,
+                      int32_t width, const int32_t* seqs_host, int32_t n_seqs, const int32_t* tok_slot);
+int tgis_k_head_norm_gate(const float* o, int32_t ldo, int32_t heads, int32_t vdim, const float* w, const float* gate, int32_t ldg,
+                          int32_t act, float eps, void* out, int32_t out_dt, int32_t T);
+/* resid += rmsnorm((rmsnorm(y_main) * w_main + rmsnorm(y_pair) * w_pair) / 2) * w_post; out = rmsnorm(resid) * w_pre, or the
+ * stream itself in the operand type (w_pre NULL, cast_out != 0) */
+int tgis_k_resid_tail_pair(const float* y_main, const float* y_pair, const float* w_main, const float* w_pair,
+                           const float* w_post, const float* w_pre, float* resid, void* out, int32_t out_dt, int32_t cast_out,
+                           float eps, int32_t T, int32_t hidden);
+
 #ifdef __cplusplus
 }
 #endif

@@ -606,4 +606,110 @@ int tgis_k_moe_align(const int32_t* ids, int32_t T, int32_t top, int32_t E, int3
   return 0;
 }
 
+static CapAttnGeom to_cap(const tgis_k_capattn_geom* g) {
+  return CapAttnGeom{g->heads, g->kv_heads, g->dim, g->vdim, g->scale, g->softcap, g->qt_coef, g->qt_every};
+}
+static void host_seqs(const int32_t* seqs_host, int n_seqs, std::vector<AttnSeq>& seqs) {
+  seqs.resize(n_seqs);
+  for (int i = 0; i < n_seqs; ++i) seqs[i] = AttnSeq{seqs_host[4 * i], seqs_host[4 * i + 1], seqs_host[4 * i + 2], seqs_host[4 * i + 3]};
+}
+
+int tgis_k_capattn_prep(const float* y, int32_t ldy, int32_t q_off, int32_t k_off, int32_t v_off, const tgis_k_capattn_geom* g,
+                        const float* w_q, const float* w_k, float eps, const int32_t* positions, const int32_t* slots,
+                        void* q_out, void* k_cache, void* v_cache, int32_t dt, int32_t T) {
+  KCK(capattn_prep_launch(y, ldy, q_off, k_off, v_off, to_cap(g), w_q, w_k, eps, positions, slots, q_out, k_cache, v_cache, dt, T, 0));
+  KCK(cudaDeviceSynchronize());
+  return 0;
+}
+
+int tgis_k_capattn(const void* q, const void* k_cache, const void* v_cache, int32_t dt, const int32_t* seqs_host, int32_t n_seqs,
+                   const int32_t* block_table_host, int32_t bt_rows, int32_t bt_stride, const float* gate, int32_t gate_ld,
+                   void* out, const tgis_k_capattn_geom* g) {
+  std::vector<AttnSeq> seqs;
+  host_seqs(seqs_host, n_seqs, seqs);
+  std::vector<LatentTile> tiles;
+  for (int i = 0; i < n_seqs; ++i)
+    for (int q0 = 0; q0 < seqs[i].q_len; q0 += CAPATTN_TILE) tiles.push_back(LatentTile{i, q0, std::min(CAPATTN_TILE, seqs[i].q_len - q0), 0});
+  Tmp<AttnSeq> d_seqs;
+  Tmp<LatentTile> d_tiles;
+  Tmp<int32_t> d_bt;
+  KCK(d_seqs.upload(seqs.data(), seqs.size()));
+  KCK(d_tiles.upload(tiles.data(), tiles.size()));
+  KCK(d_bt.upload(block_table_host, (size_t)bt_rows * bt_stride));
+  KCK(capattn_launch(q, k_cache, v_cache, dt, d_seqs.p, d_tiles.p, (int)tiles.size(), d_bt.p, bt_stride, gate, gate_ld, out, dt,
+                     to_cap(g), 0));
+  KCK(cudaDeviceSynchronize());
+  return 0;
+}
+
+int tgis_k_token_shift(const float* x, int32_t width, const float* mu, int32_t n_mix, const int32_t* positions,
+                       const int32_t* tok_slot, const float* prev_state, void* out, int32_t out_dt, int64_t out_bs, int32_t T) {
+  KCK(token_shift_mix_launch(x, width, mu, n_mix, positions, tok_slot, prev_state, out, out_dt, out_bs, T, 0));
+  KCK(cudaDeviceSynchronize());
+  return 0;
+}
+
+int tgis_k_short_conv(const float* xz, int32_t ld, int32_t inner, const float* w, const float* b, int32_t taps,
+                      const int32_t* positions, const int32_t* tok_slot, const float* conv_state, float* out_f32, void* out_op,
+                      int32_t out_dt, int32_t T) {
+  KCK(short_conv_silu_launch(xz, ld, inner, w, b, taps, positions, tok_slot, conv_state, out_f32, out_op, out_dt, T, 0));
+  KCK(cudaDeviceSynchronize());
+  return 0;
+}
+
+int tgis_k_selective_scan(const float* x, const float* xz, int32_t ld_xz, const float* proj, int32_t ld_proj, int32_t dt_rank,
+                          const float* dt_raw, const float* dt_b, const float* A_log, const float* D, float* S,
+                          float* conv_state, void* out, int32_t out_dt, int32_t inner, int32_t state, int32_t taps,
+                          const int32_t* seqs_host, int32_t n_seqs, const int32_t* tok_slot) {
+  std::vector<AttnSeq> seqs;
+  host_seqs(seqs_host, n_seqs, seqs);
+  Tmp<AttnSeq> d_seqs;
+  KCK(d_seqs.upload(seqs.data(), seqs.size()));
+  SelScan a{};
+  a.x = x; a.xz = xz; a.ld_xz = ld_xz; a.proj = proj; a.ld_proj = ld_proj; a.dt_rank = dt_rank; a.dt_raw = dt_raw; a.dt_b = dt_b;
+  a.A_log = A_log; a.D = D; a.S = S; a.conv_state = conv_state; a.out = out; a.out_dtype = out_dt; a.inner = inner;
+  a.state = state; a.taps = taps;
+  KCK(selective_scan_launch(a, d_seqs.p, n_seqs, tok_slot, 0));
+  KCK(cudaDeviceSynchronize());
+  return 0;
+}
+
+int tgis_k_outer_scan(int32_t mode, const float* q, const float* k, const float* v, int32_t ldq, int32_t ldk, int32_t ldv,
+                      float q_scale, const float* decay_raw, int32_t ldd, const float* w0, const float* u, const float* ig,
+                      const float* fg, int32_t ldg, const float* ig_b, const float* fg_b, float gate_cap, float* S, float* n,
+                      float* m, float* out, int32_t ldo, int32_t heads, int32_t dim, int32_t vdim, const float* x, float* x_last,
+                      int32_t width, const int32_t* seqs_host, int32_t n_seqs, const int32_t* tok_slot) {
+  std::vector<AttnSeq> seqs;
+  host_seqs(seqs_host, n_seqs, seqs);
+  Tmp<AttnSeq> d_seqs;
+  KCK(d_seqs.upload(seqs.data(), seqs.size()));
+  OuterScan a{};
+  a.mode = mode; a.q = q; a.k = k; a.v = v; a.ldq = ldq; a.ldk = ldk; a.ldv = ldv; a.q_scale = q_scale;
+  a.decay_raw = decay_raw; a.ldd = ldd; a.w0 = w0; a.u = u;
+  a.ig = ig; a.fg = fg; a.ldg = ldg; a.ig_b = ig_b; a.fg_b = fg_b; a.gate_cap = gate_cap;
+  a.S = S; a.n = n; a.m = m; a.out = out; a.ldo = ldo; a.heads = heads; a.dim = dim; a.vdim = vdim;
+  a.x = x; a.x_last = x_last; a.width = width;
+  KCK(outer_scan_launch(a, d_seqs.p, n_seqs, tok_slot, 0));
+  KCK(cudaDeviceSynchronize());
+  return 0;
+}
+
+int tgis_k_head_norm_gate(const float* o, int32_t ldo, int32_t heads, int32_t vdim, const float* w, const float* gate, int32_t ldg,
+                          int32_t act, float eps, void* out, int32_t out_dt, int32_t T) {
+  KCK(head_norm_gate_launch(o, ldo, heads, vdim, w, gate, ldg, act, eps, out, out_dt, T, 0));
+  KCK(cudaDeviceSynchronize());
+  return 0;
+}
+
+int tgis_k_resid_tail_pair(const float* y_main, const float* y_pair, const float* w_main, const float* w_pair,
+                           const float* w_post, const float* w_pre, float* resid, void* out, int32_t out_dt, int32_t cast_out,
+                           float eps, int32_t T, int32_t hidden) {
+  ResidTail a{};
+  a.y_main = y_main; a.y_pair = y_pair; a.w_main = w_main; a.w_pair = w_pair; a.w_post = w_post; a.w_pre = w_pre;
+  a.resid = resid; a.out = out; a.out_dtype = out_dt; a.cast_out = cast_out; a.mult = 1.f; a.w_off = 0.f; a.eps = eps;
+  KCK(resid_tail_launch(a, T, hidden, 0));
+  KCK(cudaDeviceSynchronize());
+  return 0;
+}
+
 }  // extern "C"
