@@ -770,10 +770,11 @@ def run_ours(args) -> dict | None:
 
 
 # ------------------------------------------------------------------------------------------------ --arch-compare
-# Prefill and decode throughput of the Ponenex family beside the closest existing family (Llama) at equal hidden size, layer
+# Prefill and decode throughput of the layer-list families (Ponenex, Falerax) beside the closest existing family (Llama) at equal hidden size, layer
 # count and active feed-forward width, random weights, device-timed (the engine's CUDA events around every step).  Not the
 # default workload: `python bench.py --arch-compare` prints its own JSON line; the default JSON line is untouched.
-ARCH_COMPARE = [("ponenex-1k", "llama-cmp-1k"), ("ponenex-2k", "llama-cmp-2k")]
+ARCH_COMPARE = [("ponenex-1k", "llama-cmp-1k"), ("ponenex-2k", "llama-cmp-2k"), ("falerax-1k", "llama-cmp-1k"),
+                ("falerax-2k", "llama-cmp-2k")]
 
 
 def _arch_work(mc, B: int, ctx: float) -> tuple[float, float]:
@@ -793,6 +794,25 @@ def _arch_work(mc, B: int, ctx: float) -> tuple[float, float]:
             bytes_ += 2.0 * (dense + per_head + 3 * h * (experts_touched * l.expert_ff + l.shared_ff) + h * (l.experts + 1))
             bytes_ += 2.0 * B * keys * row
         return flops + 2.0 * h * v, bytes_ + 2.0 * h * v
+    if mc.arch == "falerax":
+        flops = bytes_ = 0.0
+        for l in mc.layers:
+            if l.kind == "wkv":
+                a = l.heads * l.dim
+                dense, scan, state, cache = 5 * a * h + l.decay_rank * (h + a), 2 * a * l.dim, a * l.dim, 0
+            elif l.kind == "parallel":
+                mm = l.mm_heads * (l.mm_dim + l.mm_vdim)
+                dense = h * (l.heads * (l.dim + 2 * l.vdim) + l.kv_heads * (l.dim + l.vdim) + 2 * mm + 2 * l.mm_heads
+                             + l.mm_heads * l.mm_vdim)
+                scan = l.heads * ctx * (l.dim + l.vdim) + 2 * l.mm_heads * l.mm_dim * l.mm_vdim
+                state, cache = l.mm_heads * l.mm_dim * l.mm_vdim, l.kv_heads * (l.dim + l.vdim)
+            else:
+                dense = 3 * l.inner * h + (2 * l.dt_rank + 2 * l.state) * l.inner
+                scan, state, cache = 3 * l.inner * l.state, l.inner * l.state, 0
+            flops += 2.0 * (dense + scan + 3 * h * l.ff)
+            # a decode step streams the weights once, every sequence's cache rows, and reads + writes its fp32 state
+            bytes_ += 2.0 * (dense + 3 * h * l.ff) + B * (2.0 * ctx * cache + 8.0 * state)
+        return flops + 2.0 * h * v, bytes_ + 2.0 * h * v
     qd, kvd = mc.n_q_heads * 128, mc.n_kv_heads * 128
     per_layer = h * (qd + 2 * kvd) + qd * h + 3 * h * mc.ffn
     flops = mc.n_layers * 2.0 * (per_layer + mc.n_q_heads * ctx * 2 * 128) + 2.0 * h * v
@@ -807,7 +827,10 @@ def run_arch_compare(args) -> None:
 
     from vllm_tgis_adapter_b200.engine.core import PRESETS, NativeEngine, cache_block_bytes, make_sampling_params
     from vllm_tgis_adapter_b200.engine.loader import load_synthetic_weights, rope_cos_sin
+    from vllm_tgis_adapter_b200.engine.falerax import PRESETS as FLX
     from vllm_tgis_adapter_b200.engine.ponenex import PRESETS as PNX
+
+    PNX = {**PNX, **FLX}   # the presets of the layer-list families
 
     torch.cuda.set_device(0)
     hbm_gbs, _ = peaks()

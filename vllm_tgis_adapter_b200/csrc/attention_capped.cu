@@ -2,7 +2,8 @@
 // that grows with the position, and a tanh soft cap on the scores (kernels.h: CapAttnGeom).  No rotation.
 //
 //   capattn_prep_kernel   per token: RMS norm of every query and key head (fp32), the query temperature, the cache write
-//   capattn_kernel        one CTA per (tile of CAPATTN_TILE query tokens of one sequence, query head): the sequence's
+//   capattn_mma_kernel    the same walk on the tensor cores for bf16 rows whose sizes fit the MMA tiles (see below)
+//   capattn_kernel        (fp32 rows, any sizes; FMA pipe) one CTA per (tile of CAPATTN_TILE query tokens of one sequence, query head): the sequence's
 //                         cache blocks are walked in ascending order from block 0, scores and the running softmax
 //                         (maximum, sum, accumulators) are fp32, masked keys weigh exactly zero
 //
@@ -12,6 +13,7 @@
 // operand type (bf16 when serving, fp32 in the all-fp32 mode); the block ids are the engine's.
 #include <cmath>
 #include <cstdint>
+#include <cstdlib>
 
 #include "kernels.h"
 #include "launch.cuh"
@@ -192,6 +194,196 @@ capattn_kernel(const CT* __restrict__ q, const CT* __restrict__ k_cache, const C
   }
 }
 
+// ---- tensor-core variant: bf16 queries and cache rows, dim a multiple of 16 (<= 16 MMA_KS), vdim a multiple of 8 (<= 32 MMA_NT
+// per warp).  Both products on mma.sync m16n8k16 with fp32 accumulators: the tile's 16 queries are the M rows; for the scores
+// each of the four warps owns 8 of a block's 32 keys (the query's A fragments stay in registers for the whole walk, the key
+// rows are B fragments as they lie), for the weighted sum each warp owns every fourth group of 8 value columns (value rows
+// through ldmatrix.trans).  Scale, soft cap, mask and the running softmax are fp32 on the accumulator fragments; the
+// weights are rounded to bf16 once and the SAME rounded numbers are summed for the normaliser.  Rows padded by 16 bytes keep
+// every fragment load free of bank conflicts.  A row's arithmetic does not depend on the other rows of its tile.
+constexpr int MMA_KS = 8, MMA_NT = 8;
+__device__ __forceinline__ void ca_ldsm_x4(uint32_t (&r)[4], const void* smem) {
+  const uint32_t a = (uint32_t)__cvta_generic_to_shared(smem);
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];\n"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(a));
+}
+__device__ __forceinline__ void ca_ldsm_x2(uint32_t (&r)[2], const void* smem) {
+  const uint32_t a = (uint32_t)__cvta_generic_to_shared(smem);
+  asm volatile("ldmatrix.sync.aligned.m8n8.x2.shared.b16 {%0,%1}, [%2];\n" : "=r"(r[0]), "=r"(r[1]) : "r"(a));
+}
+__device__ __forceinline__ void ca_ldsm_x4_trans(uint32_t (&r)[4], const void* smem) {
+  const uint32_t a = (uint32_t)__cvta_generic_to_shared(smem);
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];\n"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(a));
+}
+__device__ __forceinline__ void ca_mma(float (&c)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
+  asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};\n"
+               : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+               : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+
+__global__ void __launch_bounds__(CA_THREADS)
+capattn_mma_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __restrict__ k_cache,
+                   const __nv_bfloat16* __restrict__ v_cache, const AttnSeq* __restrict__ seqs,
+                   const LatentTile* __restrict__ tiles, const int32_t* __restrict__ block_table, int bt_stride,
+                   const float* __restrict__ gate, int gate_ld, __nv_bfloat16* __restrict__ out, CapAttnGeom g) {
+  using bf = __nv_bfloat16;
+  extern __shared__ __align__(16) uint8_t cam_smem[];
+  const int d = g.dim, dv = g.vdim, LDK = d + 8, LDV = dv + 8, LDP = KV_BLOCK + 8;
+  bf* Qs = reinterpret_cast<bf*>(cam_smem);            // [16][LDK]
+  bf* Ks = Qs + CA_QT * LDK;                           // [32][LDK]
+  bf* Vs = Ks + KV_BLOCK * LDK;                        // [32][LDV]
+  bf* Ps = Vs + KV_BLOCK * LDV;                        // [16][LDP]
+  float* smax = reinterpret_cast<float*>(Ps + CA_QT * LDP);   // [4][16]; reused for the final row sums
+  griddep_launch();
+  griddep_wait();
+  const LatentTile tl = tiles[blockIdx.x];
+  const AttnSeq sq = seqs[tl.seq];
+  const int h = blockIdx.y, kvh = h / (g.heads / g.kv_heads);
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, gq = lane >> 2, t2 = (lane & 3) * 2;
+  const int row0 = sq.q_start + tl.q0, pos0 = sq.kv_len - sq.q_len + tl.q0, nq = tl.nq;
+  const int dch = d / 8, vch = dv / 8;   // 16-byte chunks per row
+  for (int i = tid; i < CA_QT * dch; i += CA_THREADS) {
+    const int qi = i / dch, ch = i % dch;
+    uint4 v = make_uint4(0, 0, 0, 0);
+    if (qi < nq) v = *reinterpret_cast<const uint4*>(q + ((size_t)(row0 + qi) * g.heads + h) * d + ch * 8);
+    *reinterpret_cast<uint4*>(Qs + qi * LDK + ch * 8) = v;
+  }
+  __syncthreads();
+  const int nks = d / 16;
+  uint32_t qa[MMA_KS][4];
+#pragma unroll
+  for (int ks = 0; ks < MMA_KS; ++ks)
+    if (ks < nks) ca_ldsm_x4(qa[ks], Qs + (size_t)(lane & 15) * LDK + ks * 16 + (lane >> 4) * 8);
+  float acc[MMA_NT][4];
+#pragma unroll
+  for (int j = 0; j < MMA_NT; ++j) acc[j][0] = acc[j][1] = acc[j][2] = acc[j][3] = 0.f;
+  float m_run[2] = {-INFINITY, -INFINITY}, l_part[2] = {0.f, 0.f};   // rows gq and gq + 8
+  const int n_blocks = (pos0 + nq - 1) / KV_BLOCK + 1;
+  const int32_t* bt = block_table + (size_t)sq.block_row * bt_stride;
+  const float inv_cap = g.softcap > 0.f ? 1.f / g.softcap : 0.f;
+  for (int b = 0; b < n_blocks; ++b) {
+    const size_t blk = (size_t)bt[b];
+    __syncthreads();   // the previous block's tiles are consumed
+    for (int i = tid; i < KV_BLOCK * dch; i += CA_THREADS) {
+      const int j = i / dch, ch = i % dch;
+      *reinterpret_cast<uint4*>(Ks + j * LDK + ch * 8) =
+          *reinterpret_cast<const uint4*>(k_cache + ((blk * KV_BLOCK + j) * g.kv_heads + kvh) * d + ch * 8);
+    }
+    for (int i = tid; i < KV_BLOCK * vch; i += CA_THREADS) {
+      const int j = i / vch, ch = i % vch;
+      *reinterpret_cast<uint4*>(Vs + j * LDV + ch * 8) =
+          *reinterpret_cast<const uint4*>(v_cache + ((blk * KV_BLOCK + j) * g.kv_heads + kvh) * dv + ch * 8);
+    }
+    __syncthreads();
+    // ---- scores of this warp's 8 keys
+    float c[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+    for (int ks = 0; ks < MMA_KS; ++ks)
+      if (ks < nks) {
+        uint32_t kb[2];
+        ca_ldsm_x2(kb, Ks + (size_t)(warp * 8 + (lane & 7)) * LDK + ks * 16 + ((lane >> 3) & 1) * 8);
+        ca_mma(c, qa[ks], kb[0], kb[1]);
+      }
+    bool ok[4];
+#pragma unroll
+    for (int e = 0; e < 4; ++e) {
+      const int qi = gq + (e >> 1) * 8, kpos = b * KV_BLOCK + warp * 8 + t2 + (e & 1);
+      ok[e] = qi < nq && kpos <= pos0 + qi;
+      float sc = c[e] * g.scale;
+      if (g.softcap > 0.f) sc = g.softcap * tanhf(sc * inv_cap);
+      c[e] = ok[e] ? sc : -INFINITY;
+    }
+    float mx[2] = {fmaxf(c[0], c[1]), fmaxf(c[2], c[3])};
+#pragma unroll
+    for (int r = 0; r < 2; ++r) {
+      mx[r] = fmaxf(mx[r], __shfl_xor_sync(0xffffffffu, mx[r], 1));
+      mx[r] = fmaxf(mx[r], __shfl_xor_sync(0xffffffffu, mx[r], 2));
+    }
+    if ((lane & 3) == 0) {
+      smax[warp * CA_QT + gq] = mx[0];
+      smax[warp * CA_QT + gq + 8] = mx[1];
+    }
+    __syncthreads();
+    float al[2];
+#pragma unroll
+    for (int r = 0; r < 2; ++r) {
+      const int qi = gq + r * 8;
+      const float bm = fmaxf(fmaxf(smax[qi], smax[CA_QT + qi]), fmaxf(smax[2 * CA_QT + qi], smax[3 * CA_QT + qi]));
+      const float m_new = fmaxf(m_run[r], bm);
+      al[r] = m_new == -INFINITY ? 1.f : expf(m_run[r] - m_new);
+      const bf p0 = __float2bfloat16_rn(ok[2 * r] ? expf(c[2 * r] - m_new) : 0.f);
+      const bf p1 = __float2bfloat16_rn(ok[2 * r + 1] ? expf(c[2 * r + 1] - m_new) : 0.f);
+      l_part[r] = fmaf(l_part[r], al[r], __bfloat162float(p0) + __bfloat162float(p1));
+      m_run[r] = m_new;
+      __nv_bfloat162 pk;
+      pk.x = p0; pk.y = p1;
+      *reinterpret_cast<__nv_bfloat162*>(Ps + qi * LDP + warp * 8 + t2) = pk;
+    }
+    __syncthreads();
+    // ---- weighted sum of the values: this warp's groups of 8 columns
+    uint32_t a0[4], a1[4];
+    ca_ldsm_x4(a0, Ps + (size_t)(lane & 15) * LDP + (lane >> 4) * 8);
+    ca_ldsm_x4(a1, Ps + (size_t)(lane & 15) * LDP + 16 + (lane >> 4) * 8);
+#pragma unroll
+    for (int j = 0; j < MMA_NT; ++j) {
+      const int n0 = (warp + 4 * j) * 8;
+      if (n0 < dv) {
+        acc[j][0] *= al[0]; acc[j][1] *= al[0]; acc[j][2] *= al[1]; acc[j][3] *= al[1];
+        uint32_t vb[4];
+        ca_ldsm_x4_trans(vb, Vs + (size_t)lane * LDV + n0);
+        ca_mma(acc[j], a0, vb[0], vb[1]);
+        ca_mma(acc[j], a1, vb[2], vb[3]);
+      }
+    }
+  }
+  // ---- row sums: over the quad, then over the warps
+#pragma unroll
+  for (int r = 0; r < 2; ++r) {
+    l_part[r] += __shfl_xor_sync(0xffffffffu, l_part[r], 1);
+    l_part[r] += __shfl_xor_sync(0xffffffffu, l_part[r], 2);
+  }
+  __syncthreads();
+  if ((lane & 3) == 0) {
+    smax[warp * CA_QT + gq] = l_part[0];
+    smax[warp * CA_QT + gq + 8] = l_part[1];
+  }
+  __syncthreads();
+#pragma unroll
+  for (int r = 0; r < 2; ++r) {
+    const int qi = gq + r * 8;
+    if (qi >= nq) continue;
+    const float inv_l = 1.f / (smax[qi] + smax[CA_QT + qi] + smax[2 * CA_QT + qi] + smax[3 * CA_QT + qi]);
+    const size_t row = (size_t)(row0 + qi);
+#pragma unroll
+    for (int j = 0; j < MMA_NT; ++j) {
+      const int n = (warp + 4 * j) * 8 + t2;
+      if (n < dv) {
+        float o0 = acc[j][2 * r] * inv_l, o1 = acc[j][2 * r + 1] * inv_l;
+        if (gate != nullptr) {
+          const float* gr = gate + row * gate_ld + (size_t)h * dv + n;
+          o0 *= 1.f / (1.f + expf(-gr[0]));
+          o1 *= 1.f / (1.f + expf(-gr[1]));
+        }
+        __nv_bfloat162 pk;
+        pk.x = __float2bfloat16_rn(o0); pk.y = __float2bfloat16_rn(o1);
+        *reinterpret_cast<__nv_bfloat162*>(out + (row * g.heads + h) * dv + n) = pk;
+      }
+    }
+  }
+}
+
+bool capattn_mma_eligible(const CapAttnGeom& g, const void* q, const void* k_cache, const void* v_cache, const void* out) {
+  static int on = -1;
+  if (on < 0) {
+    const char* e = getenv("TGIS_CAPATTN_MMA");   // 0: the FMA kernel for every shape (A/B and the tests)
+    on = (e && e[0] == '0') ? 0 : 1;
+  }
+  auto al16 = [](const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; };
+  return on == 1 && g.dim % 16 == 0 && g.dim <= 16 * MMA_KS && g.vdim % 8 == 0 && g.vdim <= 32 * MMA_NT && al16(q) &&
+         al16(k_cache) && al16(v_cache) && al16(out);
+}
+
 size_t capattn_smem(const CapAttnGeom& g) {
   return ((size_t)CA_QT * g.dim + (size_t)KV_BLOCK * (g.dim + 1) + (size_t)KV_BLOCK * g.vdim + CA_QT * KV_BLOCK + 2 * CA_QT) *
          sizeof(float);
@@ -239,6 +431,13 @@ cudaError_t capattn_launch(const void* q, const void* k_cache, const void* v_cac
       g.vdim > CAPATTN_MAX_VDIM || capattn_smem(g) > 200 * 1024 || out_dtype != dtype)
     return cudaErrorInvalidValue;
   using bf = __nv_bfloat16;
+  if (dtype == DT_BF16 && capattn_mma_eligible(g, q, k_cache, v_cache, out)) {
+    const size_t smem = ((size_t)(CA_QT + KV_BLOCK) * (g.dim + 8) + (size_t)KV_BLOCK * (g.vdim + 8) + CA_QT * (KV_BLOCK + 8)) * sizeof(bf) +
+                        4 * CA_QT * sizeof(float);   // <= 35 KB
+    return launch_k(capattn_mma_kernel, dim3(n_tiles, g.heads), dim3(CA_THREADS), smem, stream, reinterpret_cast<const bf*>(q),
+                    reinterpret_cast<const bf*>(k_cache), reinterpret_cast<const bf*>(v_cache), seqs, tiles, block_table, bt_stride,
+                    gate, gate_ld, reinterpret_cast<bf*>(out), g);
+  }
   if (dtype == DT_BF16)
     return capattn_launch_t<bf, bf>(q, k_cache, v_cache, seqs, tiles, n_tiles, block_table, bt_stride, gate, gate_ld, out, g, stream);
   return capattn_launch_t<float, float>(q, k_cache, v_cache, seqs, tiles, n_tiles, block_table, bt_stride, gate, gate_ld, out, g, stream);

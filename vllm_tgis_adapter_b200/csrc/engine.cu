@@ -1542,7 +1542,7 @@ struct tgis_engine {
   void pnx_gemm(const void* X, int x_dt, int ldx, const void* Wt, void* Y, int y_dt, int ldy, int T, int N, int K,
                 int mode = GEMM_ANY_PLAIN, bool x_tma_ok = true) {
     if (pnx_tc && x_tma_ok && pnx_dt == DT_BF16 && x_dt == DT_BF16 && ldx == K && K % 64 == 0 && K >= 256 && N % 8 == 0 &&
-        N >= 128 && !cfg.debug_gemm_ref) {
+        N >= 128 && !cfg.debug_gemm_ref && (reinterpret_cast<uintptr_t>(Y) & 15) == 0 && (reinterpret_cast<uintptr_t>(X) & 15) == 0) {
       const int out_mode = mode == GEMM_ANY_SWIGLU && y_dt == DT_BF16 ? 2 : mode == GEMM_ANY_GEGLU && y_dt == DT_BF16 ? 3
                            : mode == GEMM_ANY_PLAIN ? (y_dt == DT_F32 ? 1 : 0) : -1;
       if (out_mode >= 0 && pnx_gemm_tc(X, Wt, Y, ldy, T, N, K, out_mode)) return;

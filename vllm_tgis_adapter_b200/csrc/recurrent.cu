@@ -79,14 +79,18 @@ short_conv_silu_kernel(const float* __restrict__ xz, int ld, int inner, const fl
 }
 
 // ------------------------------------------------------------------------------------------------ selective scan
-constexpr int SCAN_THREADS = 64, SCAN_CHUNK = 8;
+constexpr int SCAN_THREADS = 64, SCAN_CHUNK = 8, SCAN_REG_STATE = 16;
+// REG: the channel's state entries and decay rates live in registers (state <= SCAN_REG_STATE), otherwise in shared memory.
+// A chunk's B / C rows are staged in shared memory and its per-channel scalars (step size, input, gate) are fetched ahead
+// of the chunk's arithmetic, so the token loop waits for memory once per chunk, not once per token.
+template <bool REG>
 __global__ void __launch_bounds__(SCAN_THREADS)
 selective_scan_kernel(SelScan a, const AttnSeq* __restrict__ seqs, const int32_t* __restrict__ tok_slot) {
   extern __shared__ float scan_smem[];
   const int N = a.state;
-  float* Ss = scan_smem;                          // [N][SCAN_THREADS]
-  float* As = Ss + (size_t)N * SCAN_THREADS;      // [N][SCAN_THREADS]
-  float* BC = As + (size_t)N * SCAN_THREADS;      // [SCAN_CHUNK][2 N]
+  float* BC = scan_smem;                                         // [SCAN_CHUNK][2 N]
+  float* Ss = BC + (size_t)SCAN_CHUNK * 2 * N;                   // !REG: [N][SCAN_THREADS]
+  float* As = Ss + (REG ? 0 : (size_t)N * SCAN_THREADS);         // !REG: [N][SCAN_THREADS]
   griddep_launch();
   griddep_wait();
   const AttnSeq sq = seqs[blockIdx.x];
@@ -95,9 +99,18 @@ selective_scan_kernel(SelScan a, const AttnSeq* __restrict__ seqs, const int32_t
   const int slot = tok_slot[sq.q_start];
   const int first = sq.kv_len - sq.q_len;   // position of the portion's first token
   float* Sg = a.S + ((size_t)slot * a.inner + (live ? c : 0)) * N;
-  for (int n = 0; n < N; ++n) {
-    Ss[n * SCAN_THREADS + tid] = (live && first > 0) ? Sg[n] : 0.f;
-    As[n * SCAN_THREADS + tid] = live ? -expf(a.A_log[(size_t)c * N + n]) : 0.f;
+  float Sr[SCAN_REG_STATE], Ar[SCAN_REG_STATE];
+  if (REG) {
+#pragma unroll
+    for (int n = 0; n < SCAN_REG_STATE; ++n) {
+      Sr[n] = (live && first > 0 && n < N) ? Sg[n] : 0.f;
+      Ar[n] = (live && n < N) ? -expf(a.A_log[(size_t)c * N + n]) : 0.f;
+    }
+  } else {
+    for (int n = 0; n < N; ++n) {
+      Ss[n * SCAN_THREADS + tid] = (live && first > 0) ? Sg[n] : 0.f;
+      As[n * SCAN_THREADS + tid] = live ? -expf(a.A_log[(size_t)c * N + n]) : 0.f;
+    }
   }
   const float dtb = live ? a.dt_b[c] : 0.f, Dc = live ? a.D[c] : 0.f;
   for (int t0 = 0; t0 < sq.q_len; t0 += SCAN_CHUNK) {
@@ -107,27 +120,52 @@ selective_scan_kernel(SelScan a, const AttnSeq* __restrict__ seqs, const int32_t
       const int tt = i / (2 * N), j = i % (2 * N);
       BC[i] = a.proj[(size_t)(sq.q_start + t0 + tt) * a.ld_proj + a.dt_rank + j];
     }
+    float dtv[SCAN_CHUNK], xv[SCAN_CHUNK], zv[SCAN_CHUNK];
+#pragma unroll
+    for (int tt = 0; tt < SCAN_CHUNK; ++tt) {
+      const size_t row = (size_t)(sq.q_start + t0 + tt);
+      const bool ok = live && tt < nt;
+      dtv[tt] = ok ? a.dt_raw[row * a.inner + c] : 0.f;
+      xv[tt] = ok ? a.x[row * a.inner + c] : 0.f;
+      zv[tt] = ok ? a.xz[row * a.ld_xz + a.inner + c] : 0.f;
+    }
     __syncthreads();
     if (!live) continue;
-    for (int tt = 0; tt < nt; ++tt) {
-      const size_t row = (size_t)(sq.q_start + t0 + tt);
-      const float dt = softplus_f(a.dt_raw[row * a.inner + c] + dtb);
-      const float xv = a.x[row * a.inner + c];
-      const float dx = dt * xv;
-      const float* Bt = BC + (size_t)tt * 2 * N;
-      float y = 0.f;
-      for (int n = 0; n < N; ++n) {
-        const float s = fmaf(expf(dt * As[n * SCAN_THREADS + tid]), Ss[n * SCAN_THREADS + tid], dx * Bt[n]);
-        Ss[n * SCAN_THREADS + tid] = s;
-        y = fmaf(s, Bt[N + n], y);
+#pragma unroll
+    for (int tt = 0; tt < SCAN_CHUNK; ++tt) {
+      if (tt < nt) {
+        const size_t row = (size_t)(sq.q_start + t0 + tt);
+        const float dt = softplus_f(dtv[tt] + dtb);
+        const float dx = dt * xv[tt];
+        const float* Bt = BC + (size_t)tt * 2 * N;
+        float y = 0.f;
+        if (REG) {
+#pragma unroll
+          for (int n = 0; n < SCAN_REG_STATE; ++n)
+            if (n < N) {
+              Sr[n] = fmaf(expf(dt * Ar[n]), Sr[n], dx * Bt[n]);
+              y = fmaf(Sr[n], Bt[N + n], y);
+            }
+        } else {
+          for (int n = 0; n < N; ++n) {
+            const float sv = fmaf(expf(dt * As[n * SCAN_THREADS + tid]), Ss[n * SCAN_THREADS + tid], dx * Bt[n]);
+            Ss[n * SCAN_THREADS + tid] = sv;
+            y = fmaf(sv, Bt[N + n], y);
+          }
+        }
+        y = fmaf(Dc, xv[tt], y);
+        st_op(a.out, a.out_dtype, row * a.inner + c, y * silu_f(zv[tt]));
       }
-      y = fmaf(Dc, xv, y);
-      const float z = a.xz[row * a.ld_xz + a.inner + c];
-      st_op(a.out, a.out_dtype, row * a.inner + c, y * silu_f(z));
     }
   }
   if (!live) return;
-  for (int n = 0; n < N; ++n) Sg[n] = Ss[n * SCAN_THREADS + tid];
+  if (REG) {
+#pragma unroll
+    for (int n = 0; n < SCAN_REG_STATE; ++n)
+      if (n < N) Sg[n] = Sr[n];
+  } else {
+    for (int n = 0; n < N; ++n) Sg[n] = Ss[n * SCAN_THREADS + tid];
+  }
   // the convolution's tail: inputs of the last taps - 1 positions (entry e: position end - (taps - 1) + e)
   const int K1 = a.taps - 1;
   float* cs = a.conv_state + (size_t)slot * K1 * a.inner + c;
@@ -142,24 +180,26 @@ selective_scan_kernel(SelScan a, const AttnSeq* __restrict__ seqs, const int32_t
 
 // ------------------------------------------------------------------------------------------------ outer-product memories
 // grid (sequences, heads, ceil(vdim / 32)); 256 threads = 8 row groups (warps) x 32 value columns (lanes).  Thread (g, c)
-// keeps rows g, g + 8, ... of column c in registers; a token's q / k / decay vectors are staged in shared memory one token
-// ahead; the row groups' partial sums meet in shared memory and warp 0 writes the token's outputs.
-constexpr int OS_GROUPS = 8, OS_COLS = 32, OS_THREADS = OS_GROUPS * OS_COLS;
+// keeps rows g, g + 8, ... of column c in registers.  The tokens' q / k / decay vectors, value columns and gates are staged
+// in shared memory OS_CHUNK tokens at a time (one wait for memory per chunk); per token the row groups' partial sums meet in
+// shared memory (double-buffered: one barrier per token) and warp 0 writes the token's outputs.
+constexpr int OS_GROUPS = 8, OS_COLS = 32, OS_THREADS = OS_GROUPS * OS_COLS, OS_CHUNK = 8;
 template <int RPT, int MODE>
 __global__ void __launch_bounds__(OS_THREADS)
 outer_scan_kernel(OuterScan a, const AttnSeq* __restrict__ seqs, const int32_t* __restrict__ tok_slot) {
-  __shared__ float vec[2][3][OUTER_SCAN_MAX_DIM];   // [buffer][q | k | w][dim]
-  __shared__ float nvec[OUTER_SCAN_MAX_DIM];        // GATED: the normaliser n
-  __shared__ float part[OS_GROUPS][OS_COLS + 1];
-  __shared__ float part_n[OS_GROUPS];
-  __shared__ float gates[2][2];                     // GATED: raw (i, f) of the staged token
+  extern __shared__ float os_smem[];
+  const int D = a.dim;
+  float* vec = os_smem;                                  // [OS_CHUNK][3][D]: q | k | w
+  float* vcol = vec + (size_t)OS_CHUNK * 3 * D;          // [OS_CHUNK][OS_COLS]
+  __shared__ float part[2][OS_GROUPS][OS_COLS + 1];
+  __shared__ float part_n[2][OS_GROUPS];
+  __shared__ float gates[OS_CHUNK][2];                   // GATED: capped log input gate, log forget gate
   griddep_launch();
   griddep_wait();
   const AttnSeq sq = seqs[blockIdx.x];
   const int h = blockIdx.y, tid = threadIdx.x, g = tid >> 5, lane = tid & 31;
-  const int c = blockIdx.z * OS_COLS + lane;
+  const int c0 = blockIdx.z * OS_COLS, c = c0 + lane;
   const bool col_ok = c < a.vdim;
-  const int D = a.dim;
   const int slot = tok_slot[sq.q_start];
   const bool fresh = sq.kv_len - sq.q_len == 0;
   float S[RPT];
@@ -169,7 +209,7 @@ outer_scan_kernel(OuterScan a, const AttnSeq* __restrict__ seqs, const int32_t* 
     const int i = g + j * OS_GROUPS;
     S[j] = (!fresh && col_ok && i < D) ? Sg[(size_t)i * a.vdim] : 0.f;
   }
-  float u_r[RPT];
+  float u_r[RPT];   // DECAY: the bonus u of this thread's rows; GATED: the normaliser n of its rows (the same in every lane)
   float m_run = 0.f;
   if (MODE == OUTER_SCAN_DECAY) {
 #pragma unroll
@@ -178,75 +218,83 @@ outer_scan_kernel(OuterScan a, const AttnSeq* __restrict__ seqs, const int32_t* 
       u_r[j] = i < D ? a.u[(size_t)h * D + i] : 0.f;
     }
   } else {
-    float* ng = a.n + ((size_t)slot * a.heads + h) * D;
-    for (int i = tid; i < D; i += OS_THREADS) nvec[i] = fresh ? 0.f : ng[i];
+    const float* ng = a.n + ((size_t)slot * a.heads + h) * D;
+#pragma unroll
+    for (int j = 0; j < RPT; ++j) {
+      const int i = g + j * OS_GROUPS;
+      u_r[j] = (!fresh && i < D) ? ng[i] : 0.f;
+    }
     m_run = fresh ? 0.f : a.m[(size_t)slot * a.heads + h];
   }
-  auto stage = [&](int tt, int buf) {   // token tt of the portion -> vec[buf]
-    const size_t row = (size_t)(sq.q_start + tt);
-    for (int i = tid; i < D; i += OS_THREADS) {
-      vec[buf][0][i] = a.q[row * a.ldq + (size_t)h * D + i] * a.q_scale;
-      vec[buf][1][i] = a.k[row * a.ldk + (size_t)h * D + i];
+  for (int t0 = 0; t0 < sq.q_len; t0 += OS_CHUNK) {
+    const int nt = min(OS_CHUNK, sq.q_len - t0);
+    __syncthreads();   // the previous chunk's vectors are consumed
+    for (int idx = tid; idx < nt * D; idx += OS_THREADS) {
+      const int tt = idx / D, i = idx % D;
+      const size_t row = (size_t)(sq.q_start + t0 + tt);
+      float* v3 = vec + (size_t)tt * 3 * D;
+      v3[i] = a.q[row * a.ldq + (size_t)h * D + i] * a.q_scale;
+      v3[D + i] = a.k[row * a.ldk + (size_t)h * D + i];
       if (MODE == OUTER_SCAN_DECAY)
-        vec[buf][2][i] = expf(-expf(a.decay_raw[row * a.ldd + (size_t)h * D + i] + a.w0[(size_t)h * D + i]));
+        v3[2 * D + i] = expf(-expf(a.decay_raw[row * a.ldd + (size_t)h * D + i] + a.w0[(size_t)h * D + i]));
     }
-    if (MODE == OUTER_SCAN_GATED && tid == 0) {
-      gates[buf][0] = a.ig[row * a.ldg + h] + a.ig_b[h];
-      gates[buf][1] = a.fg[row * a.ldg + h] + a.fg_b[h];
+    {
+      const int tt = tid >> 5;   // OS_THREADS / 32 == OS_CHUNK rows of value columns
+      if (tt < nt) vcol[tt * OS_COLS + lane] = col_ok ? a.v[(size_t)(sq.q_start + t0 + tt) * a.ldv + (size_t)h * a.vdim + c] : 0.f;
     }
-  };
-  stage(0, 0);
-  for (int tt = 0; tt < sq.q_len; ++tt) {
-    const int buf = tt & 1;
-    __syncthreads();   // vec[buf] (and nvec) complete; part of the previous token consumed
-    const size_t row = (size_t)(sq.q_start + tt);
-    const float vc = col_ok ? a.v[row * a.ldv + (size_t)h * a.vdim + c] : 0.f;
-    float o = 0.f, nq = 0.f;
-    if (MODE == OUTER_SCAN_DECAY) {
-#pragma unroll
-      for (int j = 0; j < RPT; ++j) {
-        const int i = g + j * OS_GROUPS;
-        if (i < D) {
-          const float kv = vec[buf][1][i] * vc;
-          o = fmaf(vec[buf][0][i], fmaf(u_r[j], kv, S[j]), o);
-          S[j] = fmaf(vec[buf][2][i], S[j], kv);
-        }
-      }
-    } else {
-      const float ig = a.gate_cap * tanhf(gates[buf][0] / a.gate_cap);
-      const float fg = logsigmoid_f(a.gate_cap * tanhf(gates[buf][1] / a.gate_cap));
-      const float m_new = fmaxf(fg + m_run, ig);
-      const float da = expf(fg + m_run - m_new), db = expf(ig - m_new);
-      m_run = m_new;
-#pragma unroll
-      for (int j = 0; j < RPT; ++j) {
-        const int i = g + j * OS_GROUPS;
-        if (i < D) {
-          const float kk = vec[buf][1][i], qq = vec[buf][0][i];
-          S[j] = fmaf(da, S[j], db * kk * vc);
-          o = fmaf(qq, S[j], o);
-          const float nn = fmaf(da, nvec[i], db * kk);   // every lane of the row group computes the same value
-          nq = fmaf(nn, qq, nq);
-          __syncwarp();   // (i is uniform over the warp) every lane has read nvec[i] before lane 0 replaces it
-          if (lane == 0) nvec[i] = nn;
-        }
-      }
-      if (lane == 0) part_n[g] = nq;
+    if (MODE == OUTER_SCAN_GATED && tid < nt) {
+      const size_t row = (size_t)(sq.q_start + t0 + tid);
+      gates[tid][0] = a.gate_cap * tanhf((a.ig[row * a.ldg + h] + a.ig_b[h]) / a.gate_cap);
+      gates[tid][1] = logsigmoid_f(a.gate_cap * tanhf((a.fg[row * a.ldg + h] + a.fg_b[h]) / a.gate_cap));
     }
-    part[g][lane] = o;
-    if (tt + 1 < sq.q_len) stage(tt + 1, buf ^ 1);
     __syncthreads();
-    if (g == 0) {
-      float s = 0.f;
+    for (int tt = 0; tt < nt; ++tt) {
+      const int par = tt & 1;
+      const float* v3 = vec + (size_t)tt * 3 * D;
+      const float vc = vcol[tt * OS_COLS + lane];
+      float o = 0.f, nq = 0.f;
+      if (MODE == OUTER_SCAN_DECAY) {
 #pragma unroll
-      for (int r = 0; r < OS_GROUPS; ++r) s += part[r][lane];
-      if (MODE == OUTER_SCAN_GATED) {
-        float d = 0.f;
+        for (int j = 0; j < RPT; ++j) {
+          const int i = g + j * OS_GROUPS;
+          if (i < D) {
+            const float kv = v3[D + i] * vc;
+            o = fmaf(v3[i], fmaf(u_r[j], kv, S[j]), o);
+            S[j] = fmaf(v3[2 * D + i], S[j], kv);
+          }
+        }
+      } else {
+        const float ig = gates[tt][0], fg = gates[tt][1];
+        const float m_new = fmaxf(fg + m_run, ig);
+        const float da = expf(fg + m_run - m_new), db = expf(ig - m_new);
+        m_run = m_new;
 #pragma unroll
-        for (int r = 0; r < OS_GROUPS; ++r) d += part_n[r];
-        s = s / (fmaxf(fabsf(d), expf(-m_run)) + 1e-6f);
+        for (int j = 0; j < RPT; ++j) {
+          const int i = g + j * OS_GROUPS;
+          if (i < D) {
+            const float kk = v3[D + i], qq = v3[i];
+            S[j] = fmaf(da, S[j], db * kk * vc);
+            o = fmaf(qq, S[j], o);
+            u_r[j] = fmaf(da, u_r[j], db * kk);
+            nq = fmaf(u_r[j], qq, nq);
+          }
+        }
+        if (lane == 0) part_n[par][g] = nq;
       }
-      if (col_ok) a.out[row * a.ldo + (size_t)h * a.vdim + c] = s;
+      part[par][g][lane] = o;
+      __syncthreads();   // partials of token tt complete; buffer par is rewritten only two tokens (two barriers) later
+      if (g == 0) {
+        float sum = 0.f;
+#pragma unroll
+        for (int r = 0; r < OS_GROUPS; ++r) sum += part[par][r][lane];
+        if (MODE == OUTER_SCAN_GATED) {
+          float d = 0.f;
+#pragma unroll
+          for (int r = 0; r < OS_GROUPS; ++r) d += part_n[par][r];
+          sum = sum / (fmaxf(fabsf(d), expf(-m_run)) + 1e-6f);
+        }
+        if (col_ok) a.out[(size_t)(sq.q_start + t0 + tt) * a.ldo + (size_t)h * a.vdim + c] = sum;
+      }
     }
   }
   // ---- leave the state behind the portion's last token
@@ -259,9 +307,14 @@ outer_scan_kernel(OuterScan a, const AttnSeq* __restrict__ seqs, const int32_t* 
   }
   if (blockIdx.z == 0) {
     if (MODE == OUTER_SCAN_GATED) {
-      __syncthreads();
       float* ng = a.n + ((size_t)slot * a.heads + h) * D;
-      for (int i = tid; i < D; i += OS_THREADS) ng[i] = nvec[i];
+      if (lane == 0) {
+#pragma unroll
+        for (int j = 0; j < RPT; ++j) {
+          const int i = g + j * OS_GROUPS;
+          if (i < D) ng[i] = u_r[j];
+        }
+      }
       if (tid == 0) a.m[(size_t)slot * a.heads + h] = m_run;
     }
     if (a.x_last != nullptr && h == 0) {
@@ -324,24 +377,27 @@ cudaError_t selective_scan_launch(const SelScan& a, const AttnSeq* seqs, int n_s
                                   cudaStream_t stream) {
   if (n_seqs <= 0) return cudaSuccess;
   if (a.state < 1 || a.state > SELSCAN_MAX_STATE || a.taps < 1) return cudaErrorInvalidValue;
-  const size_t smem = ((size_t)2 * a.state * SCAN_THREADS + (size_t)SCAN_CHUNK * 2 * a.state) * sizeof(float);
+  const dim3 grid(n_seqs, (a.inner + SCAN_THREADS - 1) / SCAN_THREADS);
+  const size_t bc = (size_t)SCAN_CHUNK * 2 * a.state * sizeof(float);
+  if (a.state <= SCAN_REG_STATE) return launch_k(selective_scan_kernel<true>, grid, dim3(SCAN_THREADS), bc, stream, a, seqs, tok_slot);
+  const size_t smem = bc + (size_t)2 * a.state * SCAN_THREADS * sizeof(float);
   static size_t smem_set = 0;
   if (smem > 48 * 1024 && smem > smem_set) {
-    const cudaError_t e = cudaFuncSetAttribute(selective_scan_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    const cudaError_t e = cudaFuncSetAttribute(selective_scan_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return e;
     smem_set = smem;
   }
-  return launch_k(selective_scan_kernel, dim3(n_seqs, (a.inner + SCAN_THREADS - 1) / SCAN_THREADS), dim3(SCAN_THREADS), smem,
-                  stream, a, seqs, tok_slot);
+  return launch_k(selective_scan_kernel<false>, grid, dim3(SCAN_THREADS), smem, stream, a, seqs, tok_slot);
 }
 
 template <int MODE>
 static cudaError_t outer_scan_mode(const OuterScan& a, const AttnSeq* seqs, int n_seqs, const int32_t* tok_slot,
                                    cudaStream_t stream) {
   const dim3 grid(n_seqs, a.heads, (a.vdim + OS_COLS - 1) / OS_COLS);
-  if (a.dim <= 8 * OS_GROUPS) return launch_k(outer_scan_kernel<8, MODE>, grid, dim3(OS_THREADS), 0, stream, a, seqs, tok_slot);
-  if (a.dim <= 16 * OS_GROUPS) return launch_k(outer_scan_kernel<16, MODE>, grid, dim3(OS_THREADS), 0, stream, a, seqs, tok_slot);
-  return launch_k(outer_scan_kernel<32, MODE>, grid, dim3(OS_THREADS), 0, stream, a, seqs, tok_slot);
+  const size_t smem = ((size_t)OS_CHUNK * 3 * a.dim + OS_CHUNK * OS_COLS) * sizeof(float);   // <= 25 KB
+  if (a.dim <= 8 * OS_GROUPS) return launch_k(outer_scan_kernel<8, MODE>, grid, dim3(OS_THREADS), smem, stream, a, seqs, tok_slot);
+  if (a.dim <= 16 * OS_GROUPS) return launch_k(outer_scan_kernel<16, MODE>, grid, dim3(OS_THREADS), smem, stream, a, seqs, tok_slot);
+  return launch_k(outer_scan_kernel<32, MODE>, grid, dim3(OS_THREADS), smem, stream, a, seqs, tok_slot);
 }
 cudaError_t outer_scan_launch(const OuterScan& a, const AttnSeq* seqs, int n_seqs, const int32_t* tok_slot,
                               cudaStream_t stream) {
