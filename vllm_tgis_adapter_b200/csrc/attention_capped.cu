@@ -197,7 +197,7 @@ capattn_kernel(const CT* __restrict__ q, const CT* __restrict__ k_cache, const C
 // ---- tensor-core variant: bf16 queries and cache rows, dim a multiple of 16 (<= 16 MMA_KS), vdim a multiple of 8 (<= 32 MMA_NT
 // per warp).  Both products on mma.sync m16n8k16 with fp32 accumulators: the tile's 16 queries are the M rows; for the scores
 // each of the four warps owns 8 of a block's 32 keys (the query's A fragments stay in registers for the whole walk, the key
-// rows are B fragments as they lie), for the weighted sum each warp owns every fourth group of 8 value columns (value rows
+// rows are B fragments as they lie; the block after the current one lands in a second buffer through cp.async meanwhile), for the weighted sum each warp owns every fourth group of 8 value columns (value rows
 // through ldmatrix.trans).  Scale, soft cap, mask and the running softmax are fp32 on the accumulator fragments; the
 // weights are rounded to bf16 once and the SAME rounded numbers are summed for the normaliser.  Rows padded by 16 bytes keep
 // every fragment load free of bank conflicts.  A row's arithmetic does not depend on the other rows of its tile.
@@ -216,6 +216,10 @@ __device__ __forceinline__ void ca_ldsm_x4_trans(uint32_t (&r)[4], const void* s
   asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];\n"
                : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(a));
 }
+__device__ __forceinline__ void ca_cp_async16(void* smem, const void* gmem) {
+  const uint32_t a = (uint32_t)__cvta_generic_to_shared(smem);
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16;\n" ::"r"(a), "l"(gmem) : "memory");
+}
 __device__ __forceinline__ void ca_mma(float (&c)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
   asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};\n"
                : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
@@ -231,9 +235,9 @@ capattn_mma_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __r
   extern __shared__ __align__(16) uint8_t cam_smem[];
   const int d = g.dim, dv = g.vdim, LDK = d + 8, LDV = dv + 8, LDP = KV_BLOCK + 8;
   bf* Qs = reinterpret_cast<bf*>(cam_smem);            // [16][LDK]
-  bf* Ks = Qs + CA_QT * LDK;                           // [32][LDK]
-  bf* Vs = Ks + KV_BLOCK * LDK;                        // [32][LDV]
-  bf* Ps = Vs + KV_BLOCK * LDV;                        // [16][LDP]
+  bf* Ks2 = Qs + CA_QT * LDK;                          // [2][32][LDK]   two blocks: one in use, the next one landing
+  bf* Vs2 = Ks2 + 2 * KV_BLOCK * LDK;                  // [2][32][LDV]
+  bf* Ps = Vs2 + 2 * KV_BLOCK * LDV;                   // [16][LDP]
   float* smax = reinterpret_cast<float*>(Ps + CA_QT * LDP);   // [4][16]; reused for the final row sums
   griddep_launch();
   griddep_wait();
@@ -262,20 +266,33 @@ capattn_mma_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __r
   const int n_blocks = (pos0 + nq - 1) / KV_BLOCK + 1;
   const int32_t* bt = block_table + (size_t)sq.block_row * bt_stride;
   const float inv_cap = g.softcap > 0.f ? 1.f / g.softcap : 0.f;
-  for (int b = 0; b < n_blocks; ++b) {
+  // block b's K and V rows -> buffer b & 1, as 16-byte asynchronous copies (one commit group per block)
+  auto fetch = [&](int b) {
     const size_t blk = (size_t)bt[b];
-    __syncthreads();   // the previous block's tiles are consumed
+    bf* Kd = Ks2 + (size_t)(b & 1) * KV_BLOCK * LDK;
+    bf* Vd = Vs2 + (size_t)(b & 1) * KV_BLOCK * LDV;
     for (int i = tid; i < KV_BLOCK * dch; i += CA_THREADS) {
       const int j = i / dch, ch = i % dch;
-      *reinterpret_cast<uint4*>(Ks + j * LDK + ch * 8) =
-          *reinterpret_cast<const uint4*>(k_cache + ((blk * KV_BLOCK + j) * g.kv_heads + kvh) * d + ch * 8);
+      ca_cp_async16(Kd + j * LDK + ch * 8, k_cache + ((blk * KV_BLOCK + j) * g.kv_heads + kvh) * d + ch * 8);
     }
     for (int i = tid; i < KV_BLOCK * vch; i += CA_THREADS) {
       const int j = i / vch, ch = i % vch;
-      *reinterpret_cast<uint4*>(Vs + j * LDV + ch * 8) =
-          *reinterpret_cast<const uint4*>(v_cache + ((blk * KV_BLOCK + j) * g.kv_heads + kvh) * dv + ch * 8);
+      ca_cp_async16(Vd + j * LDV + ch * 8, v_cache + ((blk * KV_BLOCK + j) * g.kv_heads + kvh) * dv + ch * 8);
     }
-    __syncthreads();
+    asm volatile("cp.async.commit_group;\n" ::: "memory");
+  };
+  fetch(0);
+  for (int b = 0; b < n_blocks; ++b) {
+    // the other buffer was last read in the previous pass, which ended with a barrier
+    if (b + 1 < n_blocks) {
+      fetch(b + 1);
+      asm volatile("cp.async.wait_group 1;\n" ::: "memory");
+    } else {
+      asm volatile("cp.async.wait_group 0;\n" ::: "memory");
+    }
+    __syncthreads();   // every thread's copies of block b have landed
+    const bf* Ks = Ks2 + (size_t)(b & 1) * KV_BLOCK * LDK;
+    const bf* Vs = Vs2 + (size_t)(b & 1) * KV_BLOCK * LDV;
     // ---- scores of this warp's 8 keys
     float c[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
@@ -336,6 +353,7 @@ capattn_mma_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __r
         ca_mma(acc[j], a1, vb[2], vb[3]);
       }
     }
+    __syncthreads();   // this pass's buffers, maxima and weights are consumed
   }
   // ---- row sums: over the quad, then over the warps
 #pragma unroll
@@ -432,8 +450,14 @@ cudaError_t capattn_launch(const void* q, const void* k_cache, const void* v_cac
     return cudaErrorInvalidValue;
   using bf = __nv_bfloat16;
   if (dtype == DT_BF16 && capattn_mma_eligible(g, q, k_cache, v_cache, out)) {
-    const size_t smem = ((size_t)(CA_QT + KV_BLOCK) * (g.dim + 8) + (size_t)KV_BLOCK * (g.vdim + 8) + CA_QT * (KV_BLOCK + 8)) * sizeof(bf) +
-                        4 * CA_QT * sizeof(float);   // <= 35 KB
+    const size_t smem = ((size_t)(CA_QT + 2 * KV_BLOCK) * (g.dim + 8) + (size_t)2 * KV_BLOCK * (g.vdim + 8) + CA_QT * (KV_BLOCK + 8)) * sizeof(bf) +
+                        4 * CA_QT * sizeof(float);   // <= 58 KB
+    static bool attr_set = false;
+    if (!attr_set) {
+      const cudaError_t e = cudaFuncSetAttribute(capattn_mma_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 64 * 1024);
+      if (e != cudaSuccess) return e;
+      attr_set = true;
+    }
     return launch_k(capattn_mma_kernel, dim3(n_tiles, g.heads), dim3(CA_THREADS), smem, stream, reinterpret_cast<const bf*>(q),
                     reinterpret_cast<const bf*>(k_cache), reinterpret_cast<const bf*>(v_cache), seqs, tiles, block_table, bt_stride,
                     gate, gate_ld, reinterpret_cast<bf*>(out), g);

@@ -79,8 +79,9 @@ short_conv_silu_kernel(const float* __restrict__ xz, int ld, int inner, const fl
 }
 
 // ------------------------------------------------------------------------------------------------ selective scan
-constexpr int SCAN_THREADS = 64, SCAN_CHUNK = 8, SCAN_REG_STATE = 16;
-// REG: the channel's state entries and decay rates live in registers (state <= SCAN_REG_STATE), otherwise in shared memory.
+constexpr int SCAN_THREADS = 64, SCAN_CHUNK = 8, SCAN_REG_STATE = 16, SCAN_LPC = 4, SCAN_RPL = SCAN_REG_STATE / SCAN_LPC;
+// REG (state <= SCAN_REG_STATE): SCAN_LPC lanes share a channel, lane `sub` keeps states sub, sub + 4, ... and their decay rates in
+// registers and the lanes' partial outputs meet through two shuffles; otherwise one thread per channel, state in shared memory.
 // A chunk's B / C rows are staged in shared memory and its per-channel scalars (step size, input, gate) are fetched ahead
 // of the chunk's arithmetic, so the token loop waits for memory once per chunk, not once per token.
 template <bool REG>
@@ -94,17 +95,20 @@ selective_scan_kernel(SelScan a, const AttnSeq* __restrict__ seqs, const int32_t
   griddep_launch();
   griddep_wait();
   const AttnSeq sq = seqs[blockIdx.x];
-  const int tid = threadIdx.x, c = blockIdx.y * SCAN_THREADS + tid;
+  const int tid = threadIdx.x;
+  const int sub = REG ? tid % SCAN_LPC : 0;
+  const int c = REG ? blockIdx.y * (SCAN_THREADS / SCAN_LPC) + tid / SCAN_LPC : blockIdx.y * SCAN_THREADS + tid;
   const bool live = c < a.inner;
   const int slot = tok_slot[sq.q_start];
   const int first = sq.kv_len - sq.q_len;   // position of the portion's first token
   float* Sg = a.S + ((size_t)slot * a.inner + (live ? c : 0)) * N;
-  float Sr[SCAN_REG_STATE], Ar[SCAN_REG_STATE];
+  float Sr[SCAN_RPL], Ar[SCAN_RPL];
   if (REG) {
 #pragma unroll
-    for (int n = 0; n < SCAN_REG_STATE; ++n) {
-      Sr[n] = (live && first > 0 && n < N) ? Sg[n] : 0.f;
-      Ar[n] = (live && n < N) ? -expf(a.A_log[(size_t)c * N + n]) : 0.f;
+    for (int j = 0; j < SCAN_RPL; ++j) {
+      const int n = sub + j * SCAN_LPC;
+      Sr[j] = (live && first > 0 && n < N) ? Sg[n] : 0.f;
+      Ar[j] = (live && n < N) ? -expf(a.A_log[(size_t)c * N + n]) : 0.f;
     }
   } else {
     for (int n = 0; n < N; ++n) {
@@ -130,7 +134,7 @@ selective_scan_kernel(SelScan a, const AttnSeq* __restrict__ seqs, const int32_t
       zv[tt] = ok ? a.xz[row * a.ld_xz + a.inner + c] : 0.f;
     }
     __syncthreads();
-    if (!live) continue;
+    if (!REG && !live) continue;   // (REG: every lane takes part in the shuffles)
 #pragma unroll
     for (int tt = 0; tt < SCAN_CHUNK; ++tt) {
       if (tt < nt) {
@@ -141,11 +145,16 @@ selective_scan_kernel(SelScan a, const AttnSeq* __restrict__ seqs, const int32_t
         float y = 0.f;
         if (REG) {
 #pragma unroll
-          for (int n = 0; n < SCAN_REG_STATE; ++n)
+          for (int j = 0; j < SCAN_RPL; ++j) {
+            const int n = sub + j * SCAN_LPC;
             if (n < N) {
-              Sr[n] = fmaf(expf(dt * Ar[n]), Sr[n], dx * Bt[n]);
-              y = fmaf(Sr[n], Bt[N + n], y);
+              Sr[j] = fmaf(expf(dt * Ar[j]), Sr[j], dx * Bt[n]);
+              y = fmaf(Sr[j], Bt[N + n], y);
             }
+          }
+          y += __shfl_xor_sync(0xffffffffu, y, 1);
+          y += __shfl_xor_sync(0xffffffffu, y, 2);
+          if (!live || sub != 0) continue;
         } else {
           for (int n = 0; n < N; ++n) {
             const float sv = fmaf(expf(dt * As[n * SCAN_THREADS + tid]), Ss[n * SCAN_THREADS + tid], dx * Bt[n]);
@@ -161,8 +170,9 @@ selective_scan_kernel(SelScan a, const AttnSeq* __restrict__ seqs, const int32_t
   if (!live) return;
   if (REG) {
 #pragma unroll
-    for (int n = 0; n < SCAN_REG_STATE; ++n)
-      if (n < N) Sg[n] = Sr[n];
+    for (int j = 0; j < SCAN_RPL; ++j)
+      if (sub + j * SCAN_LPC < N) Sg[sub + j * SCAN_LPC] = Sr[j];
+    if (sub != 0) return;
   } else {
     for (int n = 0; n < N; ++n) Sg[n] = Ss[n * SCAN_THREADS + tid];
   }
@@ -181,9 +191,11 @@ selective_scan_kernel(SelScan a, const AttnSeq* __restrict__ seqs, const int32_t
 // ------------------------------------------------------------------------------------------------ outer-product memories
 // grid (sequences, heads, ceil(vdim / 32)); 256 threads = 8 row groups (warps) x 32 value columns (lanes).  Thread (g, c)
 // keeps rows g, g + 8, ... of column c in registers.  The tokens' q / k / decay vectors, value columns and gates are staged
-// in shared memory OS_CHUNK tokens at a time (one wait for memory per chunk); per token the row groups' partial sums meet in
-// shared memory (double-buffered: one barrier per token) and warp 0 writes the token's outputs.
-constexpr int OS_GROUPS = 8, OS_COLS = 32, OS_THREADS = OS_GROUPS * OS_COLS, OS_CHUNK = 8;
+// in shared memory OS_CHUNK tokens at a time (one wait for memory per chunk).  The recurrence itself is private to a thread (its
+// rows of S, and redundantly the running maximum and its rows of n); only a token's OUTPUT sums over the row groups.  So a thread
+// runs through the chunk's tokens without any barrier, leaving its partial sums per token in shared memory, and after ONE barrier
+// warp w sums and writes the outputs of the chunk's token w.
+constexpr int OS_GROUPS = 8, OS_COLS = 32, OS_THREADS = OS_GROUPS * OS_COLS, OS_CHUNK = 16;
 template <int RPT, int MODE>
 __global__ void __launch_bounds__(OS_THREADS)
 outer_scan_kernel(OuterScan a, const AttnSeq* __restrict__ seqs, const int32_t* __restrict__ tok_slot) {
@@ -191,9 +203,11 @@ outer_scan_kernel(OuterScan a, const AttnSeq* __restrict__ seqs, const int32_t* 
   const int D = a.dim;
   float* vec = os_smem;                                  // [OS_CHUNK][3][D]: q | k | w
   float* vcol = vec + (size_t)OS_CHUNK * 3 * D;          // [OS_CHUNK][OS_COLS]
-  __shared__ float part[2][OS_GROUPS][OS_COLS + 1];
-  __shared__ float part_n[2][OS_GROUPS];
+  __shared__ float part[OS_CHUNK][OS_GROUPS][OS_COLS + 1];
+  __shared__ float part_n[OS_CHUNK][OS_GROUPS];
   __shared__ float gates[OS_CHUNK][2];                   // GATED: capped log input gate, log forget gate
+  __shared__ float floor_m[OS_CHUNK];                    // GATED: e^(-m) after each token
+  static_assert(OS_CHUNK % OS_GROUPS == 0, "warp w writes the outputs of the chunk's tokens w, w + OS_GROUPS, ...");
   griddep_launch();
   griddep_wait();
   const AttnSeq sq = seqs[blockIdx.x];
@@ -228,7 +242,7 @@ outer_scan_kernel(OuterScan a, const AttnSeq* __restrict__ seqs, const int32_t* 
   }
   for (int t0 = 0; t0 < sq.q_len; t0 += OS_CHUNK) {
     const int nt = min(OS_CHUNK, sq.q_len - t0);
-    __syncthreads();   // the previous chunk's vectors are consumed
+    __syncthreads();   // the previous chunk's vectors and partial sums are consumed
     for (int idx = tid; idx < nt * D; idx += OS_THREADS) {
       const int tt = idx / D, i = idx % D;
       const size_t row = (size_t)(sq.q_start + t0 + tt);
@@ -238,10 +252,8 @@ outer_scan_kernel(OuterScan a, const AttnSeq* __restrict__ seqs, const int32_t* 
       if (MODE == OUTER_SCAN_DECAY)
         v3[2 * D + i] = expf(-expf(a.decay_raw[row * a.ldd + (size_t)h * D + i] + a.w0[(size_t)h * D + i]));
     }
-    {
-      const int tt = tid >> 5;   // OS_THREADS / 32 == OS_CHUNK rows of value columns
-      if (tt < nt) vcol[tt * OS_COLS + lane] = col_ok ? a.v[(size_t)(sq.q_start + t0 + tt) * a.ldv + (size_t)h * a.vdim + c] : 0.f;
-    }
+    for (int tt = g; tt < nt; tt += OS_GROUPS)
+      vcol[tt * OS_COLS + lane] = col_ok ? a.v[(size_t)(sq.q_start + t0 + tt) * a.ldv + (size_t)h * a.vdim + c] : 0.f;
     if (MODE == OUTER_SCAN_GATED && tid < nt) {
       const size_t row = (size_t)(sq.q_start + t0 + tid);
       gates[tid][0] = a.gate_cap * tanhf((a.ig[row * a.ldg + h] + a.ig_b[h]) / a.gate_cap);
@@ -249,7 +261,6 @@ outer_scan_kernel(OuterScan a, const AttnSeq* __restrict__ seqs, const int32_t* 
     }
     __syncthreads();
     for (int tt = 0; tt < nt; ++tt) {
-      const int par = tt & 1;
       const float* v3 = vec + (size_t)tt * 3 * D;
       const float vc = vcol[tt * OS_COLS + lane];
       float o = 0.f, nq = 0.f;
@@ -279,22 +290,23 @@ outer_scan_kernel(OuterScan a, const AttnSeq* __restrict__ seqs, const int32_t* 
             nq = fmaf(u_r[j], qq, nq);
           }
         }
-        if (lane == 0) part_n[par][g] = nq;
+        if (lane == 0) part_n[tt][g] = nq;
+        if (tid == 0) floor_m[tt] = expf(-m_run);
       }
-      part[par][g][lane] = o;
-      __syncthreads();   // partials of token tt complete; buffer par is rewritten only two tokens (two barriers) later
-      if (g == 0) {
-        float sum = 0.f;
+      part[tt][g][lane] = o;
+    }
+    __syncthreads();   // the chunk's partial sums are complete
+    for (int tt = g; tt < nt; tt += OS_GROUPS) {   // this warp's tokens of the chunk
+      float sum = 0.f;
 #pragma unroll
-        for (int r = 0; r < OS_GROUPS; ++r) sum += part[par][r][lane];
-        if (MODE == OUTER_SCAN_GATED) {
-          float d = 0.f;
+      for (int r = 0; r < OS_GROUPS; ++r) sum += part[tt][r][lane];
+      if (MODE == OUTER_SCAN_GATED) {
+        float d = 0.f;
 #pragma unroll
-          for (int r = 0; r < OS_GROUPS; ++r) d += part_n[par][r];
-          sum = sum / (fmaxf(fabsf(d), expf(-m_run)) + 1e-6f);
-        }
-        if (col_ok) a.out[(size_t)(sq.q_start + t0 + tt) * a.ldo + (size_t)h * a.vdim + c] = sum;
+        for (int r = 0; r < OS_GROUPS; ++r) d += part_n[tt][r];
+        sum = sum / (fmaxf(fabsf(d), floor_m[tt]) + 1e-6f);
       }
+      if (col_ok) a.out[(size_t)(sq.q_start + t0 + tt) * a.ldo + (size_t)h * a.vdim + c] = sum;
     }
   }
   // ---- leave the state behind the portion's last token
@@ -377,9 +389,13 @@ cudaError_t selective_scan_launch(const SelScan& a, const AttnSeq* seqs, int n_s
                                   cudaStream_t stream) {
   if (n_seqs <= 0) return cudaSuccess;
   if (a.state < 1 || a.state > SELSCAN_MAX_STATE || a.taps < 1) return cudaErrorInvalidValue;
-  const dim3 grid(n_seqs, (a.inner + SCAN_THREADS - 1) / SCAN_THREADS);
   const size_t bc = (size_t)SCAN_CHUNK * 2 * a.state * sizeof(float);
-  if (a.state <= SCAN_REG_STATE) return launch_k(selective_scan_kernel<true>, grid, dim3(SCAN_THREADS), bc, stream, a, seqs, tok_slot);
+  if (a.state <= SCAN_REG_STATE) {
+    constexpr int per_cta = SCAN_THREADS / SCAN_LPC;
+    return launch_k(selective_scan_kernel<true>, dim3(n_seqs, (a.inner + per_cta - 1) / per_cta), dim3(SCAN_THREADS), bc, stream, a,
+                    seqs, tok_slot);
+  }
+  const dim3 grid(n_seqs, (a.inner + SCAN_THREADS - 1) / SCAN_THREADS);
   const size_t smem = bc + (size_t)2 * a.state * SCAN_THREADS * sizeof(float);
   static size_t smem_set = 0;
   if (smem > 48 * 1024 && smem > smem_set) {
@@ -394,9 +410,15 @@ template <int MODE>
 static cudaError_t outer_scan_mode(const OuterScan& a, const AttnSeq* seqs, int n_seqs, const int32_t* tok_slot,
                                    cudaStream_t stream) {
   const dim3 grid(n_seqs, a.heads, (a.vdim + OS_COLS - 1) / OS_COLS);
-  const size_t smem = ((size_t)OS_CHUNK * 3 * a.dim + OS_CHUNK * OS_COLS) * sizeof(float);   // <= 25 KB
+  const size_t smem = ((size_t)OS_CHUNK * 3 * a.dim + OS_CHUNK * OS_COLS) * sizeof(float);   // <= 50 KB (+ 18 KB static)
   if (a.dim <= 8 * OS_GROUPS) return launch_k(outer_scan_kernel<8, MODE>, grid, dim3(OS_THREADS), smem, stream, a, seqs, tok_slot);
   if (a.dim <= 16 * OS_GROUPS) return launch_k(outer_scan_kernel<16, MODE>, grid, dim3(OS_THREADS), smem, stream, a, seqs, tok_slot);
+  static bool attr_set = false;   // keys of more than 128 entries: the staged chunk passes the default 48 KB of shared memory
+  if (!attr_set) {
+    const cudaError_t e = cudaFuncSetAttribute(outer_scan_kernel<32, MODE>, cudaFuncAttributeMaxDynamicSharedMemorySize, 64 * 1024);
+    if (e != cudaSuccess) return e;
+    attr_set = true;
+  }
   return launch_k(outer_scan_kernel<32, MODE>, grid, dim3(OS_THREADS), smem, stream, a, seqs, tok_slot);
 }
 cudaError_t outer_scan_launch(const OuterScan& a, const AttnSeq* seqs, int n_seqs, const int32_t* tok_slot,
