@@ -135,6 +135,11 @@ def _cap_weights(m, wq, wk):
     dict(heads=3, kv_heads=1, dim=40, vdim=33, scale=0.2, softcap=0.0),
     dict(heads=2, kv_heads=2, dim=5, vdim=140, scale=0.5, softcap=50.0, q_temp=dict(coef=1.5, every=1)),
     dict(heads=1, kv_heads=1, dim=64, vdim=64, scale=0.125, softcap=2.0, q_temp=dict(coef=0.1, every=64)),
+    # sizes the tensor-core kernels take in bf16: one head per CTA, and the heads of a key/value head grouped in one CTA
+    dict(heads=2, kv_heads=2, dim=96, vdim=200, scale=0.1, softcap=15.0, q_temp=dict(coef=0.3, every=50)),
+    dict(heads=4, kv_heads=2, dim=32, vdim=48, scale=0.2, softcap=8.0, q_temp=dict(coef=0.3, every=20)),
+    dict(heads=8, kv_heads=1, dim=16, vdim=128, scale=0.3, softcap=0.0),
+    dict(heads=6, kv_heads=2, dim=128, vdim=8, scale=0.09, softcap=25.0),
 ])
 @pytest.mark.parametrize("dt", [F32, BF16])
 def test_capped_attention_in_portions_matches_oracle(m, dt):
@@ -149,6 +154,24 @@ def test_capped_attention_in_portions_matches_oracle(m, dt):
     for sizes in ([T], [1], [2, 33, 1, 17, 64]):
         got = _run_capattn(h, m, wq, wk, dt, sizes, seed=len(sizes))
         _close(got, ref, 1e-5 if dt == F32 else 3e-2)
+
+
+def test_capped_attention_grouped_heads_kernel_matches_oracle(monkeypatch):
+    """The variant that runs the query heads of one key/value head in one CTA (an experiment switch, off by default)."""
+    from oracle import falerax_oracle as O
+
+    monkeypatch.setenv("TGIS_CAPATTN_GROUP", "1")
+    for m in (dict(heads=4, kv_heads=2, dim=32, vdim=48, scale=0.2, softcap=8.0, q_temp=dict(coef=0.3, every=20)),
+              dict(heads=8, kv_heads=1, dim=16, vdim=128, scale=0.3, softcap=0.0),
+              dict(heads=6, kv_heads=2, dim=128, vdim=8, scale=0.09, softcap=25.0)):
+        g = torch.Generator().manual_seed(m["vdim"])
+        T = 150
+        wq, wk = 1.0 + 0.2 * torch.randn(m["dim"], generator=g), 1.0 + 0.2 * torch.randn(m["dim"], generator=g)
+        width, w = _cap_weights(m, wq, wk)
+        h = torch.randn(T, width, generator=g)
+        ref = O.capped_attention(h.double(), w, m, 1e-5)
+        for sizes in ([T], [1], [2, 33, 1, 17, 64]):
+            _close(_run_capattn(h, m, wq, wk, BF16, sizes, seed=len(sizes)), ref, 3e-2)
 
 
 @pytest.mark.parametrize("key", [0, 31, 32, 63, 64, 200, 399])

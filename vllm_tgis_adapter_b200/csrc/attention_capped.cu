@@ -3,6 +3,7 @@
 //
 //   capattn_prep_kernel   per token: RMS norm of every query and key head (fp32), the query temperature, the cache write
 //   capattn_mma_kernel    the same walk on the tensor cores for bf16 rows whose sizes fit the MMA tiles (see below)
+//   capattn_mma_group_kernel   ... with the query heads of one key/value head in one CTA (2 to 8 heads per group)
 //   capattn_kernel        (fp32 rows, any sizes; FMA pipe) one CTA per (tile of CAPATTN_TILE query tokens of one sequence, query head): the sequence's
 //                         cache blocks are walked in ascending order from block 0, scores and the running softmax
 //                         (maximum, sum, accumulators) are fp32, masked keys weigh exactly zero
@@ -41,16 +42,18 @@ __device__ __forceinline__ float warp_max_f(float v) {
   return v;
 }
 
-// grid (T, heads + kv_heads): one warp-sized CTA per (token, query or key head); block z = 1 copies the values
+// grid (T, ceil((heads + 2 kv_heads) / 4)), 128 threads: one warp per (token, query head | key head | value head)
+constexpr int PREP_WARPS = 4;
 template <class CT>
-__global__ void __launch_bounds__(32)
+__global__ void __launch_bounds__(PREP_WARPS * 32)
 capattn_prep_kernel(const float* __restrict__ y, int ldy, int q_off, int k_off, int v_off, CapAttnGeom g,
                     const float* __restrict__ w_q, const float* __restrict__ w_k, float eps,
                     const int32_t* __restrict__ positions, const int32_t* __restrict__ slot_mapping, CT* __restrict__ q_out,
                     CT* __restrict__ k_cache, CT* __restrict__ v_cache) {
   griddep_launch();
   griddep_wait();
-  const int t = blockIdx.x, hh = blockIdx.y, lane = threadIdx.x;
+  const int t = blockIdx.x, hh = blockIdx.y * PREP_WARPS + (threadIdx.x >> 5), lane = threadIdx.x & 31;
+  if (hh >= g.heads + 2 * g.kv_heads) return;
   const int slot = slot_mapping[t];
   if (hh < g.heads + g.kv_heads) {
     const bool is_q = hh < g.heads;
@@ -391,6 +394,163 @@ capattn_mma_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __r
   }
 }
 
+// ---- grouped variant: the query heads that share a key/value head run in ONE CTA, one warp per head, so a block's K and V
+// rows are fetched once per group.  A warp owns its head's whole 16 x 32 score tile: the running softmax needs no exchange
+// between warps (row maxima and sums meet over the four lanes of a quad), the weights go from the score accumulators straight
+// into the A fragments of the second product, and the only barriers are the two per block that guard the double buffer.
+// vdim <= 8 MMG_NT.  Same arithmetic per row as capattn_mma_kernel.
+constexpr int MMG_NT = 16;
+__global__ void __launch_bounds__(256)
+capattn_mma_group_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __restrict__ k_cache,
+                         const __nv_bfloat16* __restrict__ v_cache, const AttnSeq* __restrict__ seqs,
+                         const LatentTile* __restrict__ tiles, const int32_t* __restrict__ block_table, int bt_stride,
+                         const float* __restrict__ gate, int gate_ld, __nv_bfloat16* __restrict__ out, CapAttnGeom g) {
+  using bf = __nv_bfloat16;
+  extern __shared__ __align__(16) uint8_t cag_smem[];
+  const int d = g.dim, dv = g.vdim, LDK = d + 8, LDV = dv + 8;
+  bf* Ks2 = reinterpret_cast<bf*>(cag_smem);           // [2][32][LDK]
+  bf* Vs2 = Ks2 + 2 * KV_BLOCK * LDK;                  // [2][32][LDV]
+  griddep_launch();
+  griddep_wait();
+  const LatentTile tl = tiles[blockIdx.x];
+  const AttnSeq sq = seqs[tl.seq];
+  const int gs = g.heads / g.kv_heads, kvh = blockIdx.y;
+  const int tid = threadIdx.x, nthr = blockDim.x, warp = tid >> 5, lane = tid & 31, gq = lane >> 2, t2 = (lane & 3) * 2;
+  const int h = kvh * gs + warp;
+  const int row0 = sq.q_start + tl.q0, pos0 = sq.kv_len - sq.q_len + tl.q0, nq = tl.nq;
+  const int dch = d / 8, vch = dv / 8, nks = d / 16, nnt = dv / 8;
+  uint32_t qa[MMA_KS][4];
+#pragma unroll
+  for (int ks = 0; ks < MMA_KS; ++ks) {
+#pragma unroll
+    for (int e = 0; e < 4; ++e) {
+      const int qi = gq + (e & 1) * 8, col = ks * 16 + t2 + (e >> 1) * 8;
+      qa[ks][e] = (ks < nks && qi < nq) ? *reinterpret_cast<const uint32_t*>(q + ((size_t)(row0 + qi) * g.heads + h) * d + col) : 0u;
+    }
+  }
+  float acc[MMG_NT][4];
+#pragma unroll
+  for (int j = 0; j < MMG_NT; ++j) acc[j][0] = acc[j][1] = acc[j][2] = acc[j][3] = 0.f;
+  float m_run[2] = {-INFINITY, -INFINITY}, l_part[2] = {0.f, 0.f};
+  const int n_blocks = (pos0 + nq - 1) / KV_BLOCK + 1;
+  const int32_t* bt = block_table + (size_t)sq.block_row * bt_stride;
+  const float inv_cap = g.softcap > 0.f ? 1.f / g.softcap : 0.f;
+  auto fetch = [&](int b) {
+    const size_t blk = (size_t)bt[b];
+    bf* Kd = Ks2 + (size_t)(b & 1) * KV_BLOCK * LDK;
+    bf* Vd = Vs2 + (size_t)(b & 1) * KV_BLOCK * LDV;
+    for (int i = tid; i < KV_BLOCK * dch; i += nthr) {
+      const int j = i / dch, ch = i % dch;
+      ca_cp_async16(Kd + j * LDK + ch * 8, k_cache + ((blk * KV_BLOCK + j) * g.kv_heads + kvh) * d + ch * 8);
+    }
+    for (int i = tid; i < KV_BLOCK * vch; i += nthr) {
+      const int j = i / vch, ch = i % vch;
+      ca_cp_async16(Vd + j * LDV + ch * 8, v_cache + ((blk * KV_BLOCK + j) * g.kv_heads + kvh) * dv + ch * 8);
+    }
+    asm volatile("cp.async.commit_group;\n" ::: "memory");
+  };
+  fetch(0);
+  for (int b = 0; b < n_blocks; ++b) {
+    if (b + 1 < n_blocks) {
+      fetch(b + 1);
+      asm volatile("cp.async.wait_group 1;\n" ::: "memory");
+    } else {
+      asm volatile("cp.async.wait_group 0;\n" ::: "memory");
+    }
+    __syncthreads();   // every thread's copies of block b have landed
+    const bf* Ks = Ks2 + (size_t)(b & 1) * KV_BLOCK * LDK;
+    const bf* Vs = Vs2 + (size_t)(b & 1) * KV_BLOCK * LDV;
+    float sc[4][4];
+#pragma unroll
+    for (int nt = 0; nt < 4; ++nt) {
+      sc[nt][0] = sc[nt][1] = sc[nt][2] = sc[nt][3] = 0.f;
+#pragma unroll
+      for (int ks = 0; ks < MMA_KS; ++ks)
+        if (ks < nks) {
+          uint32_t kb[2];
+          ca_ldsm_x2(kb, Ks + (size_t)(nt * 8 + (lane & 7)) * LDK + ks * 16 + ((lane >> 3) & 1) * 8);
+          ca_mma(sc[nt], qa[ks], kb[0], kb[1]);
+        }
+    }
+    float mx[2] = {-INFINITY, -INFINITY};
+#pragma unroll
+    for (int nt = 0; nt < 4; ++nt)
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        const int qi = gq + (e >> 1) * 8, kpos = b * KV_BLOCK + nt * 8 + t2 + (e & 1);
+        float v = sc[nt][e] * g.scale;
+        if (g.softcap > 0.f) v = g.softcap * tanhf(v * inv_cap);
+        v = (qi < nq && kpos <= pos0 + qi) ? v : -INFINITY;
+        sc[nt][e] = v;
+        mx[e >> 1] = fmaxf(mx[e >> 1], v);
+      }
+    float al[2];
+    uint32_t pa[2][4];
+#pragma unroll
+    for (int r = 0; r < 2; ++r) {
+      mx[r] = fmaxf(mx[r], __shfl_xor_sync(0xffffffffu, mx[r], 1));
+      mx[r] = fmaxf(mx[r], __shfl_xor_sync(0xffffffffu, mx[r], 2));
+      const float m_new = fmaxf(m_run[r], mx[r]);
+      al[r] = m_new == -INFINITY ? 1.f : expf(m_run[r] - m_new);
+      float sum = 0.f;
+#pragma unroll
+      for (int nt = 0; nt < 4; ++nt) {
+        const float v0 = sc[nt][2 * r], v1 = sc[nt][2 * r + 1];
+        __nv_bfloat162 pk;
+        pk.x = __float2bfloat16_rn(v0 == -INFINITY ? 0.f : expf(v0 - m_new));
+        pk.y = __float2bfloat16_rn(v1 == -INFINITY ? 0.f : expf(v1 - m_new));
+        sum += __bfloat162float(pk.x) + __bfloat162float(pk.y);
+        // keys nt * 8 + t2 (+1) of row gq + 8 r: A fragment of k-step nt / 2, register r (low key half) or r + 2 (high half)
+        pa[nt >> 1][r + (nt & 1) * 2] = *reinterpret_cast<uint32_t*>(&pk);
+      }
+      l_part[r] = fmaf(l_part[r], al[r], sum);
+      m_run[r] = m_new;
+    }
+#pragma unroll
+    for (int j = 0; j < MMG_NT; ++j)
+      if (j < nnt) {
+        acc[j][0] *= al[0]; acc[j][1] *= al[0]; acc[j][2] *= al[1]; acc[j][3] *= al[1];
+        uint32_t vb[4];
+        ca_ldsm_x4_trans(vb, Vs + (size_t)lane * LDV + j * 8);
+        ca_mma(acc[j], pa[0], vb[0], vb[1]);
+        ca_mma(acc[j], pa[1], vb[2], vb[3]);
+      }
+    __syncthreads();   // this pass's buffer is consumed
+  }
+#pragma unroll
+  for (int r = 0; r < 2; ++r) {
+    l_part[r] += __shfl_xor_sync(0xffffffffu, l_part[r], 1);
+    l_part[r] += __shfl_xor_sync(0xffffffffu, l_part[r], 2);
+    const int qi = gq + r * 8;
+    if (qi >= nq) continue;
+    const float inv_l = 1.f / l_part[r];
+    const size_t row = (size_t)(row0 + qi);
+#pragma unroll
+    for (int j = 0; j < MMG_NT; ++j)
+      if (j < nnt) {
+        const int n = j * 8 + t2;
+        float o0 = acc[j][2 * r] * inv_l, o1 = acc[j][2 * r + 1] * inv_l;
+        if (gate != nullptr) {
+          const float* gr = gate + row * gate_ld + (size_t)h * dv + n;
+          o0 *= 1.f / (1.f + expf(-gr[0]));
+          o1 *= 1.f / (1.f + expf(-gr[1]));
+        }
+        __nv_bfloat162 pk;
+        pk.x = __float2bfloat16_rn(o0); pk.y = __float2bfloat16_rn(o1);
+        *reinterpret_cast<__nv_bfloat162*>(out + (row * g.heads + h) * dv + n) = pk;
+      }
+  }
+}
+
+// TGIS_CAPATTN_GROUP=1 routes grouped-query shapes to capattn_mma_group_kernel (read at every launch).  Off by default: measured
+// at 16 query / 4 key-value heads of 128 it is slower than one head per CTA (2048-token prefill step 172 against 148 us, a decode
+// step of 32 sequences 0.87 against 0.76 ms per step for the whole model) -- a quarter of the CTAs, each warp walking its whole
+// 16 x 32 tile alone with 162 registers, costs more than the K / V traffic it saves while the rows come out of L2.
+bool capattn_group_on() {
+  const char* e = getenv("TGIS_CAPATTN_GROUP");
+  return e != nullptr && e[0] == '1';
+}
+
 bool capattn_mma_eligible(const CapAttnGeom& g, const void* q, const void* k_cache, const void* v_cache, const void* out) {
   static int on = -1;
   if (on < 0) {
@@ -430,12 +590,12 @@ cudaError_t capattn_prep_launch(const float* y, int ldy, int q_off, int k_off, i
                                 const int32_t* slot_mapping, void* q_out, void* k_cache, void* v_cache, int dtype, int T,
                                 cudaStream_t stream) {
   if (T <= 0) return cudaSuccess;
-  const dim3 grid(T, g.heads + 2 * g.kv_heads);
+  const dim3 grid(T, (g.heads + 2 * g.kv_heads + PREP_WARPS - 1) / PREP_WARPS);
   if (dtype == DT_BF16)
-    return launch_k(capattn_prep_kernel<__nv_bfloat16>, grid, dim3(32), 0, stream, y, ldy, q_off, k_off, v_off, g, w_q, w_k,
+    return launch_k(capattn_prep_kernel<__nv_bfloat16>, grid, dim3(PREP_WARPS * 32), 0, stream, y, ldy, q_off, k_off, v_off, g, w_q, w_k,
                     eps, positions, slot_mapping, reinterpret_cast<__nv_bfloat16*>(q_out),
                     reinterpret_cast<__nv_bfloat16*>(k_cache), reinterpret_cast<__nv_bfloat16*>(v_cache));
-  return launch_k(capattn_prep_kernel<float>, grid, dim3(32), 0, stream, y, ldy, q_off, k_off, v_off, g, w_q, w_k, eps,
+  return launch_k(capattn_prep_kernel<float>, grid, dim3(PREP_WARPS * 32), 0, stream, y, ldy, q_off, k_off, v_off, g, w_q, w_k, eps,
                   positions, slot_mapping, reinterpret_cast<float*>(q_out), reinterpret_cast<float*>(k_cache),
                   reinterpret_cast<float*>(v_cache));
 }
@@ -449,6 +609,13 @@ cudaError_t capattn_launch(const void* q, const void* k_cache, const void* v_cac
       g.vdim > CAPATTN_MAX_VDIM || capattn_smem(g) > 200 * 1024 || out_dtype != dtype)
     return cudaErrorInvalidValue;
   using bf = __nv_bfloat16;
+  if (dtype == DT_BF16 && capattn_mma_eligible(g, q, k_cache, v_cache, out) && g.heads / g.kv_heads >= 2 &&
+      g.heads / g.kv_heads <= 8 && g.vdim <= 8 * MMG_NT && capattn_group_on()) {
+    const size_t smem = ((size_t)2 * KV_BLOCK * (g.dim + 8) + (size_t)2 * KV_BLOCK * (g.vdim + 8)) * sizeof(bf);   // <= 35 KB
+    return launch_k(capattn_mma_group_kernel, dim3(n_tiles, g.kv_heads), dim3(32 * (g.heads / g.kv_heads)), smem, stream,
+                    reinterpret_cast<const bf*>(q), reinterpret_cast<const bf*>(k_cache), reinterpret_cast<const bf*>(v_cache), seqs,
+                    tiles, block_table, bt_stride, gate, gate_ld, reinterpret_cast<bf*>(out), g);
+  }
   if (dtype == DT_BF16 && capattn_mma_eligible(g, q, k_cache, v_cache, out)) {
     const size_t smem = ((size_t)(CA_QT + 2 * KV_BLOCK) * (g.dim + 8) + (size_t)2 * KV_BLOCK * (g.vdim + 8) + CA_QT * (KV_BLOCK + 8)) * sizeof(bf) +
                         4 * CA_QT * sizeof(float);   // <= 58 KB

@@ -337,22 +337,20 @@ outer_scan_kernel(OuterScan a, const AttnSeq* __restrict__ seqs, const int32_t* 
 }
 
 // ------------------------------------------------------------------------------------------------ head norm + gate
+// grid (T, ceil(heads / 4)), 128 threads: one warp per (token, head)
 __global__ void __launch_bounds__(128)
-head_norm_gate_kernel(const float* __restrict__ o, int ldo, int vdim, const float* __restrict__ w,
+head_norm_gate_kernel(const float* __restrict__ o, int ldo, int heads, int vdim, const float* __restrict__ w,
                       const float* __restrict__ gate, int ldg, int act, float eps, void* __restrict__ out, int out_dtype,
                       int out_ld) {
-  __shared__ float red[4];
   griddep_launch();
   griddep_wait();
-  const int t = blockIdx.x, h = blockIdx.y;
+  const int t = blockIdx.x, h = blockIdx.y * 4 + (threadIdx.x >> 5), lane = threadIdx.x & 31;
+  if (h >= heads) return;
   const float* orow = o + (size_t)t * ldo + (size_t)h * vdim;
   float ss = 0.f;
-  for (int i = threadIdx.x; i < vdim; i += 128) ss = fmaf(orow[i], orow[i], ss);
-  ss = warp_sum_f(ss);
-  if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = ss;
-  __syncthreads();
-  const float rs = 1.f / sqrtf((red[0] + red[1] + red[2] + red[3]) / (float)vdim + eps);
-  for (int i = threadIdx.x; i < vdim; i += 128) {
+  for (int i = lane; i < vdim; i += 32) ss = fmaf(orow[i], orow[i], ss);
+  const float rs = 1.f / sqrtf(warp_sum_f(ss) / (float)vdim + eps);
+  for (int i = lane; i < vdim; i += 32) {
     const float gl = gate[(size_t)t * ldg + (size_t)h * vdim + i];
     const float gv = act == 1 ? silu_f(gl) : sigmoid_f(gl);
     st_op(out, out_dtype, (size_t)t * out_ld + (size_t)h * vdim + i, orow[i] * rs * w[(size_t)h * vdim + i] * gv);
@@ -432,8 +430,8 @@ cudaError_t outer_scan_launch(const OuterScan& a, const AttnSeq* seqs, int n_seq
 cudaError_t head_norm_gate_launch(const float* o, int ldo, int heads, int vdim, const float* w, const float* gate,
                                   int ldg, int act, float eps, void* out, int out_dtype, int T, cudaStream_t stream) {
   if (T <= 0) return cudaSuccess;
-  return launch_k(head_norm_gate_kernel, dim3(T, heads), dim3(128), 0, stream, o, ldo, vdim, w, gate, ldg, act, eps, out,
-                  out_dtype, heads * vdim);
+  return launch_k(head_norm_gate_kernel, dim3(T, (heads + 3) / 4), dim3(128), 0, stream, o, ldo, heads, vdim, w, gate, ldg, act,
+                  eps, out, out_dtype, heads * vdim);
 }
 
 cudaError_t convert_f32_launch(const float* x, void* out, int out_dtype, size_t n, cudaStream_t stream) {
