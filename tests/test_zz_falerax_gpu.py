@@ -587,3 +587,43 @@ def test_greedy_generation_through_the_scheduler_matches_oracle():
             lp = torch.log_softmax(O.forward(cfg, weights, p + toks[:-1])[len(p) - 1:], -1)
             for i, r in enumerate([r for r in recs if r.new_token is not None]):
                 assert abs(r.logprob - float(lp[i, r.new_token])) < 1e-3
+
+
+def test_trace_runner_command_line_on_a_model_directory(tmp_path):
+    """bin/trace_run on a directory with config.json + model.safetensors: the family and the decay map's rank come from the
+    files, a mixed schedule with a reused slot goes through standard input, the logits land in the output folder."""
+    import json
+    import subprocess
+    import sys
+    from pathlib import Path
+
+    from safetensors.torch import save_file
+
+    from oracle import falerax_oracle as O
+    from vllm_tgis_adapter_b200.engine.falerax import synthetic_weights
+
+    cfg = _cfg()
+    weights = synthetic_weights(_model(cfg, decay_rank=3), 71)
+    model = tmp_path / "model"
+    model.mkdir()
+    (model / "config.json").write_text(json.dumps(cfg))
+    save_file({k: v.contiguous() for k, v in weights.items()}, str(model / "model.safetensors"))
+    a, b, c = _tokens(70, 97, 1), _tokens(9, 97, 2), _tokens(40, 97, 3)
+    steps = [
+        {"step": 0, "entries": [{"id": "a", "tokens": a[:33], "want": [0, 32]}, {"id": "b", "tokens": b[:2], "want": [1]}], "end": []},
+        {"step": 1, "entries": [{"id": "b", "tokens": b[2:], "want": [6]}, {"id": "a", "tokens": a[33:69], "want": []}], "end": ["b"]},
+        {"step": 2, "entries": [{"id": "a", "tokens": a[69:], "want": [0]}, {"id": "c", "tokens": c, "want": [39]}], "end": ["a", "c"]},
+    ]
+    root = Path(__file__).resolve().parent.parent
+    for dtype, tol in (("float32", 3e-5), ("bfloat16", 0.1)):
+        out = tmp_path / f"out_{dtype}"
+        p = subprocess.run([sys.executable, str(root / "bin" / "trace_run"), "--model", str(model), "--dtype", dtype, "--out", str(out),
+                            "--max-tokens", "192"], input="".join(json.dumps(s) + "\n" for s in steps), capture_output=True,
+                           text=True, timeout=600)
+        assert p.returncode == 0, p.stderr[-2000:]
+        assert [l for l in p.stdout.splitlines() if l.startswith("done")] == ["done 0", "done 1", "done 2"]
+        ra, rb, rc = (O.forward(cfg, weights, t) for t in (a, b, c))
+        want = {0: torch.stack([ra[0], ra[32], rb[1]]), 1: rb[8:9], 2: torch.stack([ra[69], rc[39]])}
+        for n, ref in want.items():
+            got = np.fromfile(out / f"{n}.f32", dtype="<f4").reshape(-1, 97)
+            assert _rel(got, ref) < tol, (dtype, n)
